@@ -1,0 +1,14 @@
+"""B200 (sm_100a) implementation of the E5M2EffMA hot path: FP8 (E5M2 / E4M3) GEMM, GEMV, casts
+and fused Adam / AdamW behind the C interface of include/e5m2effma.h.
+
+The Python layer is a thin wrapper over that C interface (module `capi`), mirroring the
+functional interface of the reference's binding (binds/python/e5m2effma/__init__.py:58-131):
+`matmul`, `linear`, `cast`, `adam_step` and the `AdamW` optimizer.  torch is used for device
+memory and streams only.  There is no CPU path and no alternative backend: a missing library or
+a GPU other than compute capability 10.0 raises.
+"""
+from . import capi
+from .functional import AdamW, adam_step, cast, get_include, linear, matmul
+
+__version__ = "0.2.0"
+__all__ = ["capi", "matmul", "linear", "cast", "adam_step", "AdamW", "get_include", "__version__"]

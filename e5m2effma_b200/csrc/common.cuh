@@ -1,0 +1,186 @@
+// Shared device and host pieces of the sm_100a E5M2EffMA library: FP8 / BF16 / FP16 element
+// codecs built on the Blackwell conversion instructions, typed element access, the output
+// (epilogue) description shared by the GEMM and GEMV kernels, the amax reduction and the
+// host-side error state.
+//
+// Numerics contract (reference src/e5m2effma.cuh:83-124, include/e5m2effma.h:27-31): FP32
+// arithmetic without flush-to-zero, explicit single-rounding operations, FP8 encodes are
+// round-to-nearest-even saturating with every NaN -> 0x7F, BF16 encodes map every NaN to 0x7FC0.
+// The hardware converters differ from that only for NaN inputs, which are patched here.
+#pragma once
+#include <stdint.h>
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include "../../include/e5m2effma.h"
+
+namespace e5b {
+
+__host__ __device__ constexpr bool is_fp8(int t) { return t == E5MA_E5M2 || t == E5MA_E4M3; }
+__host__ __device__ constexpr int elem_bytes(int t) { return is_fp8(t) ? 1 : (t == E5MA_FP32 ? 4 : 2); }
+
+// ---- decode --------------------------------------------------------------------------------
+// Two FP8 codes (low 16 bits of w) -> two FP16 values, exact for both formats (E4M3 spans
+// 2^-9 .. 448, E5M2 is the upper byte of an FP16); Inf / NaN codes become FP16 Inf / NaN.
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t w) {
+  uint32_t r;
+  asm("{ .reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t; }" : "=r"(r) : "r"(w));
+  return r;
+}
+__device__ __forceinline__ uint32_t e5m2x2_to_f16x2(uint32_t w) { return __byte_perm(w, 0, 0x1404); }
+
+__device__ __forceinline__ float f16bits_to_f32(uint32_t h) {
+  return __half2float(__ushort_as_half((unsigned short)h));
+}
+__device__ __forceinline__ float dec_e4m3(uint32_t b) { return f16bits_to_f32(e4m3x2_to_f16x2(b & 0xFFu) & 0xFFFFu); }
+__device__ __forceinline__ float dec_e5m2(uint32_t b) { return f16bits_to_f32((b & 0xFFu) << 8); }
+__device__ __forceinline__ float dec_bf16(uint32_t h) { return __uint_as_float(h << 16); }
+
+// Four FP8 codes of format T packed in w -> four FP32 values
+template <int T>
+__device__ __forceinline__ void dec_fp8x4(uint32_t w, float v[4]) {
+  const uint32_t lo = T == E5MA_E4M3 ? e4m3x2_to_f16x2(w) : e5m2x2_to_f16x2(w);
+  const uint32_t hi = T == E5MA_E4M3 ? e4m3x2_to_f16x2(w >> 16) : e5m2x2_to_f16x2(w >> 16);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&lo));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&hi));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+// ---- encode --------------------------------------------------------------------------------
+__device__ __forceinline__ bool is_nan(float x) { return (__float_as_uint(x) & 0x7FFFFFFFu) > 0x7F800000u; }
+
+// (lo, hi) -> two FP8 codes in the low 16 bits (lo in bits 0..7).  cvt.rn.satfinite rounds to
+// nearest even and clamps finite overflow and Inf to the largest finite code; NaN is forced to 0x7F.
+template <int T>
+__device__ __forceinline__ uint32_t enc_fp8x2(float lo, float hi) {
+  uint32_t r;
+  if (T == E5MA_E4M3)
+    asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f32 t, %1, %2; cvt.u32.u16 %0, t; }" : "=r"(r) : "f"(hi), "f"(lo));
+  else
+    asm("{ .reg .b16 t; cvt.rn.satfinite.e5m2x2.f32 t, %1, %2; cvt.u32.u16 %0, t; }" : "=r"(r) : "f"(hi), "f"(lo));
+  if (is_nan(lo)) r = (r & 0xFF00u) | 0x7Fu;
+  if (is_nan(hi)) r = (r & 0x00FFu) | 0x7F00u;
+  return r;
+}
+template <int T> __device__ __forceinline__ uint32_t enc_fp8(float v) { return enc_fp8x2<T>(v, 0.f) & 0xFFu; }
+
+// (lo, hi) -> packed BF16 pair, nearest even; NaN -> 0x7FC0 (the converter alone gives 0x7FFF).
+__device__ __forceinline__ uint32_t enc_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  if (is_nan(lo)) r = (r & 0xFFFF0000u) | 0x7FC0u;
+  if (is_nan(hi)) r = (r & 0x0000FFFFu) | 0x7FC00000u;
+  return r;
+}
+__device__ __forceinline__ uint32_t enc_bf16(float v) { return enc_bf16x2(v, 0.f) & 0xFFFFu; }
+__device__ __forceinline__ uint32_t enc_f16(float v) { return __half_as_ushort(__float2half_rn(v)); }
+__device__ __forceinline__ uint32_t enc_f16x2(float lo, float hi) { return enc_f16(lo) | (enc_f16(hi) << 16); }
+
+// ---- typed scalar access ---------------------------------------------------------------------
+__device__ __forceinline__ float ld_or_one(const float *p) { return p ? *p : 1.0f; }
+
+// element i of an array of dtype t; FP8 values are multiplied by sinv (one rounding)
+__device__ __forceinline__ float load_elem(int t, const void *p, size_t i, float sinv) {
+  switch (t) {
+    case E5MA_E5M2: return __fmul_rn(dec_e5m2(((const uint8_t *)p)[i]), sinv);
+    case E5MA_E4M3: return __fmul_rn(dec_e4m3(((const uint8_t *)p)[i]), sinv);
+    case E5MA_BF16: return dec_bf16(((const uint16_t *)p)[i]);
+    case E5MA_FP16: return f16bits_to_f32(((const uint16_t *)p)[i]);
+    default: return ((const float *)p)[i];
+  }
+}
+// FP8 destinations store encode(v * qs)
+__device__ __forceinline__ void store_elem(int t, void *p, size_t i, float v, float qs) {
+  switch (t) {
+    case E5MA_E5M2: ((uint8_t *)p)[i] = (uint8_t)enc_fp8<E5MA_E5M2>(__fmul_rn(v, qs)); break;
+    case E5MA_E4M3: ((uint8_t *)p)[i] = (uint8_t)enc_fp8<E5MA_E4M3>(__fmul_rn(v, qs)); break;
+    case E5MA_BF16: ((uint16_t *)p)[i] = (uint16_t)enc_bf16(v); break;
+    case E5MA_FP16: ((uint16_t *)p)[i] = (uint16_t)enc_f16(v); break;
+    default: ((float *)p)[i] = v;
+  }
+}
+
+// ---- amax ----------------------------------------------------------------------------------
+// max |v| over a warp, then one integer atomicMax per warp: non-negative floats (Inf included)
+// order like their bit patterns; NaN never gets here because fmaxf drops it.
+__device__ __forceinline__ float warp_max(float m) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  return m;
+}
+__device__ __forceinline__ void amax_publish(float *amax, float m) {
+  if (m > 0.f) atomicMax(reinterpret_cast<int *>(amax), __float_as_int(m));
+}
+// Whole block (blockDim.x a multiple of 32, at most 1024): one atomic per block.
+__device__ __forceinline__ void block_amax(float *amax, float m) {
+  __shared__ float part[32];
+  m = warp_max(m);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) part[warp] = m;
+  __syncthreads();
+  if (warp == 0) {
+    m = lane < nw ? part[lane] : 0.f;
+    m = warp_max(m);
+    if (lane == 0) amax_publish(amax, m);
+  }
+}
+
+// ---- output description of GEMM / GEMV (reference include/e5m2effma.h:27-31) -------------------
+struct OutDesc {
+  const float *sa, *sb;   // scale_inv of FP8 A / B (NULL: 1)
+  int sa_vec, sb_vec;     // 1: one factor per row i / per column j
+  float alpha, beta;
+  const void *c; int ldc, c_dtype; const float *c_sinv;   // c == NULL: no C term
+  void *d; int ldd, d_dtype; const float *d_scale;
+  float *amax;
+  const void *bias; int bias_dtype;
+};
+
+struct OutScalars { float s, qs, csinv; };   // per-tensor factors read once per thread
+
+__device__ __forceinline__ OutScalars out_begin(const OutDesc &o) {
+  OutScalars r;
+  r.s = (o.sa_vec || o.sb_vec) ? 0.f : __fmul_rn(__fmul_rn(o.alpha, ld_or_one(o.sa)), ld_or_one(o.sb));
+  r.qs = ld_or_one(o.d_scale);
+  r.csinv = ld_or_one(o.c_sinv);
+  return r;
+}
+// (alpha * sa[i]) * sb[j]
+__device__ __forceinline__ float out_scale(const OutDesc &o, const OutScalars &r, int i, int j) {
+  if (!o.sa_vec && !o.sb_vec) return r.s;
+  const float a = o.sa_vec ? o.sa[i] : ld_or_one(o.sa), b = o.sb_vec ? o.sb[j] : ld_or_one(o.sb);
+  return __fmul_rn(__fmul_rn(o.alpha, a), b);
+}
+// v = acc*s + bias[i]; v = fma(beta, C[i,j], v): the value before conversion
+__device__ __forceinline__ float out_value(const OutDesc &o, const OutScalars &r, int i, int j, float acc) {
+  float v = __fmul_rn(acc, out_scale(o, r, i, j));
+  if (o.bias) v = __fadd_rn(v, load_elem(o.bias_dtype, o.bias, (size_t)i, 1.f));
+  if (o.c) v = __fmaf_rn(o.beta, load_elem(o.c_dtype, o.c, (size_t)j * o.ldc + i, r.csinv), v);
+  return v;
+}
+// one output through the whole epilogue; returns |v| for the amax statistic
+__device__ __forceinline__ float out_store(const OutDesc &o, const OutScalars &r, int i, int j, float acc) {
+  const float v = out_value(o, r, i, j, acc);
+  store_elem(o.d_dtype, o.d, (size_t)j * o.ldd + i, v, r.qs);
+  return fabsf(v);
+}
+
+// ---- host side -------------------------------------------------------------------------------
+void clear_error();
+e5ma_status fail(e5ma_status s, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+e5ma_status cuda_fail(cudaError_t e, const char *what);   // E5MA_OK when e == cudaSuccess
+
+struct DeviceProps { int cc; int sms; };
+// E5MA_OK and the properties of the current device when it is compute capability 10.x
+e5ma_status require_blackwell(const char *who, DeviceProps *out);
+
+// kernel launchers implemented in the other translation units
+cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx,
+                            int m, int n, int k, const OutDesc &o, int sms, cudaStream_t s);
+cudaError_t launch_gemm_simt(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const uint8_t *A, int lda,
+                             const uint8_t *B, int ldb, int m, int n, int k, const OutDesc &o, cudaStream_t s);
+// returns cudaErrorNotSupported when the problem is outside what the tensor-core kernel takes
+cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const uint8_t *A, int lda,
+                           const uint8_t *B, int ldb, int m, int n, int k, const OutDesc &o, int sms,
+                           cudaStream_t s);
+
+}  // namespace e5b

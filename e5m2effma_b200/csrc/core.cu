@@ -1,0 +1,204 @@
+// Host core of the library (error state, device gate, status strings) and e5ma_cast: a
+// vectorised single-pass conversion kernel with the amax statistic fused in.
+//
+// e5ma_cast follows reference src/e5m2effma.cu:85-101 (validation order, what scale_inv / scale /
+// amax apply to) and computes, per element, what its cast_kernel does (src/e5m2effma.cu:53-63):
+// v = src * scale_inv, amax = max |v|, dst = convert(v * scale).  The kernel itself is new: it is
+// specialised per (source, destination) dtype pair and moves 16 bytes per access.
+#include <stdarg.h>
+#include <stdio.h>
+#include <atomic>
+#include "common.cuh"
+
+namespace e5b {
+
+static thread_local char t_error[512];
+
+void clear_error() { t_error[0] = 0; }
+
+e5ma_status fail(e5ma_status s, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_error, sizeof t_error, fmt, ap);
+  va_end(ap);
+  return s;
+}
+
+e5ma_status cuda_fail(cudaError_t e, const char *what) {
+  if (e == cudaSuccess) return E5MA_OK;
+  return fail(E5MA_CUDA_ERROR, "%s: CUDA error %d (%s): %s", what, (int)e, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+// Per-device cache; entries are written once (two threads racing write the same values) and
+// published through the atomic flag.
+e5ma_status require_blackwell(const char *who, DeviceProps *out) {
+  static DeviceProps cache[64];
+  static std::atomic<int> ready[64];
+  int dev = -1;
+  const cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  DeviceProps p;
+  if (dev >= 0 && dev < 64 && ready[dev].load(std::memory_order_acquire)) {
+    p = cache[dev];
+  } else {
+    int ma = 0, mi = 0, sms = 0;
+    cudaError_t q = cudaDeviceGetAttribute(&ma, cudaDevAttrComputeCapabilityMajor, dev);
+    if (q == cudaSuccess) q = cudaDeviceGetAttribute(&mi, cudaDevAttrComputeCapabilityMinor, dev);
+    if (q == cudaSuccess) q = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (q != cudaSuccess) return cuda_fail(q, "cudaDeviceGetAttribute");
+    p.cc = ma * 10 + mi;
+    p.sms = sms;
+    if (dev >= 0 && dev < 64) { cache[dev] = p; ready[dev].store(1, std::memory_order_release); }
+  }
+  if (p.cc != 100)
+    return fail(E5MA_NOT_SUPPORTED, "%s: device %d is sm_%d; this build of the library contains sm_100a code only "
+                "(NVIDIA B200)", who, dev, p.cc);
+  if (out) *out = p;
+  return E5MA_OK;
+}
+
+// ---- cast kernel -----------------------------------------------------------------------------
+// 16 consecutive elements per step: 16-byte accesses for every dtype (FP32: four of them).
+template <int T>
+__device__ __forceinline__ void load16(const void *base, size_t i, float sinv, float v[16]) {
+  if (T == E5MA_FP32) {
+    const float4 *p = reinterpret_cast<const float4 *>(base) + i / 4;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) { const float4 a = __ldcs(p + q); v[4 * q] = a.x; v[4 * q + 1] = a.y; v[4 * q + 2] = a.z; v[4 * q + 3] = a.w; }
+  } else if (T == E5MA_BF16 || T == E5MA_FP16) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(base) + i / 8;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint4 a = __ldcs(p + q);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (T == E5MA_BF16) { v[8 * q + 2 * e] = __uint_as_float(w[e] << 16); v[8 * q + 2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u); }
+        else { const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[e])); v[8 * q + 2 * e] = f.x; v[8 * q + 2 * e + 1] = f.y; }
+      }
+    }
+  } else {
+    const uint4 a = __ldcs(reinterpret_cast<const uint4 *>(base) + i / 16);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      dec_fp8x4<T>(w[e], v + 4 * e);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) v[4 * e + q] = __fmul_rn(v[4 * e + q], sinv);
+    }
+  }
+}
+template <int T>
+__device__ __forceinline__ void store16(void *base, size_t i, float qs, const float v[16]) {
+  if (T == E5MA_FP32) {
+    float4 *p = reinterpret_cast<float4 *>(base) + i / 4;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) __stcs(p + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+  } else if (T == E5MA_BF16 || T == E5MA_FP16) {
+    uint4 *p = reinterpret_cast<uint4 *>(base) + i / 8;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        w[e] = T == E5MA_BF16 ? enc_bf16x2(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]) : enc_f16x2(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
+      __stcs(p + q, make_uint4(w[0], w[1], w[2], w[3]));
+    }
+  } else {
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      w[e] = enc_fp8x2<T>(__fmul_rn(v[4 * e], qs), __fmul_rn(v[4 * e + 1], qs)) |
+             (enc_fp8x2<T>(__fmul_rn(v[4 * e + 2], qs), __fmul_rn(v[4 * e + 3], qs)) << 16);
+    __stcs(reinterpret_cast<uint4 *>(base) + i / 16, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+}
+
+// VEC: both pointers are 16-byte aligned.  Whole 16-element groups go through the vector path in a
+// grid-stride loop; the remaining count % 16 elements (or everything when !VEC) go one at a time.
+template <int TS, int TD, bool VEC>
+__global__ void __launch_bounds__(256) cast_kernel(const void *__restrict__ src, void *__restrict__ dst, size_t count,
+                                                   const float *sinv_p, const float *scale_p, float *amax) {
+  const float sinv = ld_or_one(sinv_p), qs = ld_or_one(scale_p);
+  float mx = 0.f;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (size_t)gridDim.x * blockDim.x;
+  const size_t groups = VEC ? count / 16 : 0;
+  for (size_t gidx = tid; gidx < groups; gidx += nthr) {
+    float v[16];
+    load16<TS>(src, gidx * 16, sinv, v);
+#pragma unroll
+    for (int e = 0; e < 16; ++e) mx = fmaxf(mx, fabsf(v[e]));
+    store16<TD>(dst, gidx * 16, qs, v);
+  }
+  for (size_t i = groups * 16 + tid; i < count; i += nthr) {
+    const float v = load_elem(TS, src, i, sinv);
+    mx = fmaxf(mx, fabsf(v));
+    store_elem(TD, dst, i, v, qs);
+  }
+  if (amax) block_amax(amax, mx);
+}
+
+template <int TS, int TD>
+static cudaError_t cast_launch(const void *src, void *dst, size_t count, const float *sinv, const float *scale,
+                               float *amax, int sms, cudaStream_t s) {
+  const bool vec = (((uintptr_t)src | (uintptr_t)dst) & 15u) == 0;
+  const size_t work = vec ? count / 16 + (count % 16) : count;
+  size_t blocks = (work + 255) / 256;
+  const size_t cap = (size_t)sms * 16;   // two sweeps of full occupancy, then grid-stride
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  if (vec) cast_kernel<TS, TD, true><<<(unsigned)blocks, 256, 0, s>>>(src, dst, count, sinv, scale, amax);
+  else cast_kernel<TS, TD, false><<<(unsigned)blocks, 256, 0, s>>>(src, dst, count, sinv, scale, amax);
+  return cudaGetLastError();
+}
+
+template <int TS>
+static cudaError_t cast_dst(int td, const void *src, void *dst, size_t count, const float *sinv, const float *scale,
+                            float *amax, int sms, cudaStream_t s) {
+  switch (td) {
+    case E5MA_E4M3: return cast_launch<TS, E5MA_E4M3>(src, dst, count, sinv, scale, amax, sms, s);
+    case E5MA_BF16: return cast_launch<TS, E5MA_BF16>(src, dst, count, sinv, scale, amax, sms, s);
+    case E5MA_FP16: return cast_launch<TS, E5MA_FP16>(src, dst, count, sinv, scale, amax, sms, s);
+    case E5MA_FP32: return cast_launch<TS, E5MA_FP32>(src, dst, count, sinv, scale, amax, sms, s);
+    default: return cast_launch<TS, E5MA_E5M2>(src, dst, count, sinv, scale, amax, sms, s);
+  }
+}
+
+}  // namespace e5b
+
+extern "C" const char *e5ma_last_error(void) { return e5b::t_error; }
+
+extern "C" const char *e5ma_status_string(e5ma_status s) {
+  switch (s) {
+    case E5MA_OK: return "E5MA_OK";
+    case E5MA_INVALID_VALUE: return "E5MA_INVALID_VALUE";
+    case E5MA_NOT_SUPPORTED: return "E5MA_NOT_SUPPORTED";
+    case E5MA_CUDA_ERROR: return "E5MA_CUDA_ERROR";
+  }
+  return "unknown e5ma_status";
+}
+
+extern "C" e5ma_status e5ma_cast(const e5ma_tensor *src, const e5ma_tensor *dst, size_t count, cudaStream_t stream) {
+  using namespace e5b;
+  clear_error();
+  if (!src || !dst || !src->data || !dst->data) return fail(E5MA_INVALID_VALUE, "e5ma_cast: src / dst or their data is NULL");
+  const auto known = [](int t) { return t >= E5MA_E4M3 && t <= E5MA_E5M2; };
+  if (!known(src->dtype) || !known(dst->dtype))
+    return fail(E5MA_INVALID_VALUE, "e5ma_cast: invalid dtype (src %d, dst %d)", (int)src->dtype, (int)dst->dtype);
+  if (src->scaling != E5MA_SCALING_TENSOR || dst->scaling != E5MA_SCALING_TENSOR)
+    return fail(E5MA_INVALID_VALUE, "e5ma_cast: per-tensor scaling only");
+  if (count == 0) return E5MA_OK;
+  DeviceProps dp;
+  if (e5ma_status st = require_blackwell("e5ma_cast", &dp)) return st;
+  const float *sinv = is_fp8(src->dtype) ? src->scale_inv : nullptr;
+  const float *scale = is_fp8(dst->dtype) ? dst->scale : nullptr;
+  cudaError_t err;
+  switch (src->dtype) {
+    case E5MA_E4M3: err = cast_dst<E5MA_E4M3>(dst->dtype, src->data, dst->data, count, sinv, scale, dst->amax, dp.sms, stream); break;
+    case E5MA_BF16: err = cast_dst<E5MA_BF16>(dst->dtype, src->data, dst->data, count, sinv, scale, dst->amax, dp.sms, stream); break;
+    case E5MA_FP16: err = cast_dst<E5MA_FP16>(dst->dtype, src->data, dst->data, count, sinv, scale, dst->amax, dp.sms, stream); break;
+    case E5MA_FP32: err = cast_dst<E5MA_FP32>(dst->dtype, src->data, dst->data, count, sinv, scale, dst->amax, dp.sms, stream); break;
+    default: err = cast_dst<E5MA_E5M2>(dst->dtype, src->data, dst->data, count, sinv, scale, dst->amax, dp.sms, stream); break;
+  }
+  return cuda_fail(err, "e5ma_cast: kernel launch");
+}

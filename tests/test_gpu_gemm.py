@@ -1,0 +1,81 @@
+"""e5ma_gemm on the GPU against the oracle.
+
+Two regimes, as the interface documents them:
+  * problems that run the ascending-k CUDA-core kernel (an FP32 operand, or E5MA_FORCE_SIMT=1)
+    must match the host emulation bit for bit, padding included -- the reference's own test
+    criterion (tests/test_util.h:145-147), over its own case matrix (tests/test_gemm.cu:13-46);
+  * problems that run on the tensor cores must be within 1 ulp of the output format plus the
+    accumulation-order bound k * 2^-23 * sum|a*b|*|s|, checked on every output of every case.
+"""
+import numpy as np
+import pytest
+
+from harness import (BF16, E4M3, E5M2, FP16, FP32, GemmCase, GemmData, check_exact, check_tolerance, force_simt,
+                     reference_gemm_cases, reference_gemv_cases)
+
+pytestmark = pytest.mark.gpu
+CASES = reference_gemm_cases()
+GEMV_CASES = reference_gemv_cases()
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: c.label())
+def test_cuda_core_kernel_is_bit_exact(case):
+    force_simt(True)
+    try:
+        d = GemmData(case)
+        got, amax = d.run_gpu()
+    finally:
+        force_simt(False)
+    check_exact(d, got, amax)
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: c.label())
+def test_default_dispatch_within_tolerance(case):
+    d = GemmData(case)
+    got, amax = d.run_gpu()
+    if FP32 in (case.at, case.bt):
+        check_exact(d, got, amax)
+    else:
+        check_tolerance(d, got, amax)
+
+
+@pytest.mark.parametrize("case", GEMV_CASES, ids=lambda c: c.label())
+def test_gemv_route_within_tolerance(case):
+    d = GemmData(case)
+    got, amax = d.run_gpu()
+    if case.bt == FP32:
+        check_exact(d, got, amax)
+    else:
+        check_tolerance(d, got, amax)
+
+
+@pytest.mark.parametrize("case", GEMV_CASES[::7], ids=lambda c: c.label())
+def test_gemv_shapes_on_cuda_core_kernel_bit_exact(case):
+    force_simt(True)
+    try:
+        d = GemmData(case)
+        got, amax = d.run_gpu()
+    finally:
+        force_simt(False)
+    check_exact(d, got, amax)
+
+
+def test_k_zero_gives_bias_plus_beta_c():
+    d = GemmData(GemmCase(1, 0, 70, 33, 0, E5M2, E4M3, BF16, FP32, BF16, 1.0, 0.5, seed=5))
+    got, amax = d.run_gpu()
+    check_exact(d, got, amax)
+
+
+@pytest.mark.parametrize("n", [1, 8])
+def test_decode_gemv_shape(n):
+    """The decode configuration at reduced size: row-wise scaled E5M2 weights, BF16 x, BF16 y."""
+    d = GemmData(GemmCase(1, 0, 2048, n, 2048, E5M2, BF16, BF16, BF16, -1, 1.0, 0.0, vec=1, seed=31, tight=True))
+    got, amax = d.run_gpu()
+    check_tolerance(d, got, amax)
+
+
+def test_runs_are_deterministic():
+    d = GemmData(GemmCase(1, 0, 300, 200, 512, E5M2, E4M3, BF16, BF16, BF16, 1.0, 0.0, seed=77))
+    a, am_a = d.run_gpu()
+    b, am_b = d.run_gpu()
+    assert np.array_equal(a, b) and am_a == am_b
