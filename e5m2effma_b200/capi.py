@@ -47,6 +47,8 @@ def _load():
     lib.e5ma_status_string.argtypes = [ctypes.c_int]
     lib.e5ma_last_error.restype = ctypes.c_char_p
     lib.e5ma_last_error.argtypes = []
+    lib.e5b_gemm_fault.restype = ctypes.c_uint
+    lib.e5b_gemm_fault.argtypes = []
     return lib
 
 
@@ -59,6 +61,11 @@ def status_string(status):
 
 def last_error():
     return lib.e5ma_last_error().decode()
+
+
+def gemm_fault():
+    """Fault record of the tensor-core GEMM (0 = none); synchronises and clears it."""
+    return int(lib.e5b_gemm_fault())
 
 
 def tensor(data, dtype, scale_inv=None, scale=None, amax=None, scaling=SCALING_TENSOR):

@@ -1,6 +1,424 @@
-// placeholder until the tcgen05 kernel lands: declines every problem
+// Tensor-core GEMM for sm_100a: tcgen05.mma with TMA-fed shared-memory stages and FP32
+// accumulators in tensor memory.  Replaces the FP32-FMA tile kernel of the reference
+// (src/gemm_e5m2effma.cuh:117-233); the epilogue keeps its documented order
+// (include/e5m2effma.h:27-31).
+//
+// Shape of the kernel
+//   * One persistent CTA per SM walks over 128 x BN output tiles (BN = 256 or 128).  Rows of the
+//     tile (index i of D, contiguous in memory) are the M side of the MMA and therefore the 128
+//     lanes of tensor memory; columns j are TMEM columns.
+//   * Warp 0 (one elected lane) is the TMA producer: per k-block it brings a 128-row x 128-byte box
+//     of op(A) and a BN-row x 128-byte box of op(B) into a ring of shared-memory stages, both in
+//     the 128-byte-swizzled K-major layout the MMA reads.  Rows beyond m / n and bytes beyond k are
+//     zero-filled by TMA, so tails need no special code (k is a multiple of 16 elements, a zero
+//     byte is +0 in every operand format).
+//   * Warp 1 (one elected lane) issues the MMAs: four K = 32-byte steps per stage, accumulating into
+//     one of two TMEM buffers; tcgen05.commit hands the stage back to the producer and, after the
+//     last k-block, the accumulator to the epilogue.
+//   * Warps 2..5 are the epilogue: each owns the TMEM lane quadrant (warp index mod 4), reads 32
+//     columns at a time with tcgen05.ld and applies scale, bias, beta * C, amax and the conversion.
+//     While they drain one buffer the MMA warp already fills the other.
+//   * FP8 x FP8 (any E5M2 / E4M3 pairing) runs kind::f8f6f4, BF16 x BF16 runs kind::f16; one stage
+//     is 128 bytes of K either way (128 FP8 or 64 BF16 elements), so the two differ only in the
+//     instruction descriptor and the element type of the tensor maps.
+//   * No cluster features are used: every CTA loads its own operand boxes.
+//
+// Every wait on an mbarrier is bounded.  A wait that runs out records a fault word, raises a
+// block-wide abort flag that every role polls, and the CTA leaves through the common exit, where
+// tensor memory is released.  e5b_gemm_fault() reads the word back.
+#include <cuda.h>
 #include "common.cuh"
+
 namespace e5b {
-cudaError_t launch_gemm_tc(int, int, bool, bool, const uint8_t *, int, const uint8_t *, int, int, int, int,
-                           const OutDesc &, int, cudaStream_t) { return cudaErrorNotSupported; }
+namespace tc {
+
+constexpr int BM = 128;             // tile rows = MMA M
+constexpr int STAGE_K_BYTES = 128;  // bytes of K per stage = one swizzle row
+constexpr int MMA_K_BYTES = 32;     // bytes of K per tcgen05.mma
+constexpr int THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT = 4000000000ull;  // clock cycles (about two seconds)
+
+__device__ unsigned int g_fault;    // 0 = none; else (role << 24) | detail of the first bounded wait that ran out
+
+template <int BN> struct Cfg {
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int A_BYTES = BM * STAGE_K_BYTES;
+  static constexpr int B_BYTES = BN * STAGE_K_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN;
+  // stages + barriers + slack for the 1 KiB alignment of the first stage
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned int who) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((unsigned long long)(clock64() - t0) > WAIT_LIMIT) {
+      *abort_flag = 1;
+      atomicCAS(&g_fault, 0u, who);
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]; KIND 0: kind::f8f6f4, 1: kind::f16
+template <int KIND>
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  if (KIND == 0)
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p; }"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+  else
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the mbarrier gets one arrival once every MMA issued so far by this thread has completed
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive columns of 32-bit accumulators: thread = lane, v[c] = column c
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float v[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
+// swizzle (what a TMA box of 128 bytes x R rows produces): 8-row groups are 1024 bytes apart (SBO),
+// the leading offset is not used by swizzled K-major layouts (encoded as 1), descriptor version 1,
+// layout type 2 = 128-byte swizzle.  Addresses and offsets are in units of 16 bytes.
+__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+// Instruction descriptor: FP32 accumulator (bits 4-5 = 1), operand formats at bits 7-9 / 10-12,
+// both operands K-major (bits 15, 16 = 0), N / 8 at bits 17-22, M / 16 at bits 24-28.
+__host__ __device__ constexpr uint32_t instr_desc(int fmt_a, int fmt_b, int mdim, int ndim) {
+  return (1u << 4) | ((uint32_t)fmt_a << 7) | ((uint32_t)fmt_b << 10) | ((uint32_t)(ndim >> 3) << 17) |
+         ((uint32_t)(mdim >> 4) << 24);
+}
+
+// ---- epilogue --------------------------------------------------------------------------------
+template <int DT>
+__device__ __forceinline__ void store_out(void *d, size_t idx, float v, float qs) {
+  if (DT == E5MA_FP32) ((float *)d)[idx] = v;
+  else if (DT == E5MA_BF16) ((uint16_t *)d)[idx] = (uint16_t)enc_bf16(v);
+  else if (DT == E5MA_FP16) ((uint16_t *)d)[idx] = (uint16_t)enc_f16(v);
+  else if (DT == E5MA_E5M2) ((uint8_t *)d)[idx] = (uint8_t)enc_fp8<E5MA_E5M2>(__fmul_rn(v, qs));
+  else ((uint8_t *)d)[idx] = (uint8_t)enc_fp8<E5MA_E4M3>(__fmul_rn(v, qs));
+}
+
+// 32 accumulators of row i, columns j0 .. j0+31, through the epilogue.  Per-row terms (sa[i],
+// bias[i]) were read once by the caller; sb[j] is a broadcast load.
+template <int DT>
+__device__ __forceinline__ float drain32(const OutDesc &o, const OutScalars &r, const float acc[32], int i, int j0,
+                                         int n, float row_scale, float bias_i, bool row_ok) {
+  float mx = 0.f;
+  if (!row_ok) return mx;
+#pragma unroll
+  for (int c = 0; c < 32; ++c) {   // fully unrolled: acc[] stays in registers
+    const int j = j0 + c;
+    if (j >= n) continue;
+    float s = row_scale;
+    if (o.sb_vec) s = __fmul_rn(row_scale, o.sb[j]);
+    float v = __fmul_rn(acc[c], s);
+    if (o.bias) v = __fadd_rn(v, bias_i);
+    if (o.c) v = __fmaf_rn(o.beta, load_elem(o.c_dtype, o.c, (size_t)j * o.ldc + i, r.csinv), v);
+    mx = fmaxf(mx, fabsf(v));
+    store_out<DT>(o.d, (size_t)j * o.ldd + i, v, r.qs);
+  }
+  return mx;
+}
+
+// ---- the kernel ------------------------------------------------------------------------------
+template <int BN, int KIND, int DT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, int m, int n,
+               int k_bytes, uint32_t idesc, OutDesc o) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // stage ring at the first 1 KiB boundary (the swizzle pattern repeats every 1024 bytes)
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *after_ring = smem_raw + (ring - smem_u32(smem_raw)) + C::STAGES * C::STAGE_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(after_ring);            // full[S], empty[S], acc_full[2], acc_empty[2]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + 4);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  const auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  const auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
+  const auto acc_full = [&](int b) { return bar0 + 8u * (2 * C::STAGES + b); };
+  const auto acc_empty = [&](int b) { return bar0 + 8u * (2 * C::STAGES + 2 + b); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (m + BM - 1) / BM, tiles_n = (n + BN - 1) / BN, tiles = tiles_m * tiles_n;
+  const int kblocks = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {   // one warp allocates (and later frees) the accumulator columns
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int i0 = (t % tiles_m) * BM, j0 = (t / tiles_m) * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)kb)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+          const uint32_t sa = ring + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          // coordinates are in elements of the tensor map: the innermost one counts bytes for FP8 and
+          // 2-byte elements for BF16
+          const int kc = kb * (KIND == 0 ? STAGE_K_BYTES : STAGE_K_BYTES / 2);
+          tma_load_2d(sa, &map_a, kc, i0, full_bar(s));
+          tma_load_2d(sb, &map_b, kc, j0, full_bar(s));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++lt) {
+        const uint32_t buf = lt & 1u, use = lt >> 1;
+        if (!mbar_wait(acc_empty(buf), (use & 1u) ^ 1u, abort_flag, (2u << 24) | 0xFFFFu)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % C::STAGES;
+          const uint32_t ph = (it / C::STAGES) & 1u;
+          if (!mbar_wait(full_bar(s), ph, abort_flag, (2u << 24) | (uint32_t)kb)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = ring + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          const uint64_t da = kmajor_sw128_desc(sa), db = kmajor_sw128_desc(sb);
+#pragma unroll
+          for (int ks = 0; ks < STAGE_K_BYTES / MMA_K_BYTES; ++ks) {
+            // stepping 32 bytes along K inside the swizzled row = +2 in the 16-byte address field
+            mma_ss<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, idesc, (kb | ks) != 0);
+          }
+          mma_commit(empty_bar(s));
+        }
+        if (ok) mma_commit(acc_full(buf));
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 2..5: TMEM lane quadrant = warp % 4 ----------------
+    const int quad = warp & 3;
+    const OutScalars r = out_begin(o);
+    float mx = 0.f;
+    uint32_t lt = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++lt) {
+      const int i0 = (t % tiles_m) * BM, j0 = (t / tiles_m) * BN;
+      const uint32_t buf = lt & 1u, use = lt >> 1;
+      ok = mbar_wait(acc_full(buf), use & 1u, abort_flag, (3u << 24) | (uint32_t)quad);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int i = i0 + quad * 32 + lane;
+      const bool row_ok = i < m;
+      float row_scale = r.s, bias_i = 0.f;
+      if (row_ok) {
+        if (o.sa_vec || o.sb_vec) row_scale = __fmul_rn(o.alpha, o.sa_vec ? o.sa[i] : ld_or_one(o.sa));
+        if (o.sa_vec && !o.sb_vec) row_scale = __fmul_rn(row_scale, ld_or_one(o.sb));
+        if (o.bias) bias_i = load_elem(o.bias_dtype, o.bias, (size_t)i, 1.f);
+      }
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (j0 + c0 >= n) break;   // warp-uniform
+        float acc[32];
+        tmem_ld32(t_row + c0, acc);
+        mx = fmaxf(mx, drain32<DT>(o, r, acc, i, j0 + c0, n, row_scale, bias_i, row_ok));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty(buf));
+    }
+    if (o.amax) {
+      mx = warp_max(mx);
+      if (lane == 0) amax_publish(o.amax, mx);
+    }
+  }
+
+  // common exit: everybody meets, then the allocating warp releases tensor memory
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // give copies that may still be in flight time to land before the shared memory is reused
+    const unsigned long long t0 = clock64();
+    while ((unsigned long long)(clock64() - t0) < 2000000ull) { }
+  }
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// K-major operand: rows x k elements, row pitch ld elements; box = 128 bytes of K x box_rows rows
+static bool make_map(CUtensorMap *map, const void *base, int elem_bytes, int k, int rows, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(STAGE_K_BYTES / elem_bytes), (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  return fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+         CUDA_SUCCESS;
+}
+
+template <int BN, int KIND, int DT>
+static cudaError_t launch_cfg(const CUtensorMap &ma, const CUtensorMap &mb, int m, int n, int k_bytes, uint32_t idesc,
+                              const OutDesc &o, int sms, cudaStream_t s) {
+  using C = Cfg<BN>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_done[dev & 63]) {
+    const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, KIND, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               C::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    attr_done[dev & 63] = true;
+  }
+  const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_tc_kernel<BN, KIND, DT><<<grid, THREADS, C::SMEM_BYTES, s>>>(ma, mb, m, n, k_bytes, idesc, o);
+  return cudaGetLastError();
+}
+
+template <int BN, int KIND>
+static cudaError_t launch_dt(const CUtensorMap &ma, const CUtensorMap &mb, int m, int n, int k_bytes, uint32_t idesc,
+                             const OutDesc &o, int sms, cudaStream_t s) {
+  switch (o.d_dtype) {
+    case E5MA_BF16: return launch_cfg<BN, KIND, E5MA_BF16>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
+    case E5MA_FP32: return launch_cfg<BN, KIND, E5MA_FP32>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
+    case E5MA_FP16: return launch_cfg<BN, KIND, E5MA_FP16>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
+    case E5MA_E5M2: return launch_cfg<BN, KIND, E5MA_E5M2>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
+    default: return launch_cfg<BN, KIND, E5MA_E4M3>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
+  }
+}
+
+}  // namespace tc
+
+// Blackwell tile selection (takes the place of the reference's tuned per-architecture tables,
+// src/e5m2effma_tuned.h): 128 x 256 tiles when they fill the machine or n is wide, else 128 x 128.
+cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const uint8_t *A, int lda,
+                           const uint8_t *B, int ldb, int m, int n, int k, const OutDesc &o, int sms,
+                           cudaStream_t s) {
+  using namespace tc;
+  if (!a_kc || !b_kc || k <= 0) return cudaErrorNotSupported;
+  const bool f8 = is_fp8(a_dtype) && is_fp8(b_dtype);
+  const bool bf = a_dtype == E5MA_BF16 && b_dtype == E5MA_BF16;
+  if (!f8 && !bf) return cudaErrorNotSupported;
+  const int eb = f8 ? 1 : 2;
+  const int tiles256 = ((m + BM - 1) / BM) * ((n + 255) / 256);
+  const bool wide = n > 128 && (tiles256 >= sms || n % 256 == 0 || n > 1024);
+  const int bn = wide ? 256 : 128;
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, A, eb, k, m, lda, BM) || !make_map(&mb, B, eb, k, n, ldb, bn)) return cudaErrorNotSupported;
+  const int fa = f8 ? (a_dtype == E5MA_E5M2 ? 1 : 0) : 1, fb = f8 ? (b_dtype == E5MA_E5M2 ? 1 : 0) : 1;
+  const uint32_t idesc = instr_desc(fa, fb, BM, bn);
+  const int k_bytes = k * eb;
+  if (f8) return wide ? launch_dt<256, 0>(ma, mb, m, n, k_bytes, idesc, o, sms, s)
+                      : launch_dt<128, 0>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
+  return wide ? launch_dt<256, 1>(ma, mb, m, n, k_bytes, idesc, o, sms, s)
+              : launch_dt<128, 1>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
+}
+
+}  // namespace e5b
+
+// Reads and clears the fault word of the tensor-core GEMM on the current device (synchronises).
+// 0: no bounded wait ever ran out.  Declared in include/e5m2effma_b200.h.
+extern "C" unsigned int e5b_gemm_fault(void) {
+  unsigned int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, e5b::tc::g_fault, sizeof v) != cudaSuccess) return 0xFFFFFFFFu;
+  cudaMemcpyToSymbol(e5b::tc::g_fault, &zero, sizeof zero);
+  return v;
 }

@@ -78,9 +78,12 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_mma_kernel(const uint8_t *
   const uint8_t *xcol = X + (size_t)g * ldx * XB;
   const bool xlive = g < n;
 
-  // chunk c covers bytes [128c, 128c + 128) of every row; this lane owns 16 bytes in each half
+  // A warp's step covers bytes [kc, kc + 128) of every row; this lane owns 16 bytes in each half.
+  // The trip count must be the same for all lanes of the warp (mma.sync is warp-collective), so the
+  // loop runs on the warp-uniform kc and the per-lane offset only enters the load predicates.
 #pragma unroll 2
-  for (int kb = warp * 128 + t * 16; kb < k; kb += GV_WARPS * 128) {
+  for (int kc = warp * 128; kc < k; kc += GV_WARPS * 128) {
+    const int kb = kc + t * 16;
     uint4 wa[MT][2], wb[MT][2];
     uint32_t xw[2][8];
 #pragma unroll

@@ -20,10 +20,30 @@ def build():
     subprocess.run(["make", "-s", "-C", _HERE], check=True)
 
 
+def usable_cpus():
+    """CPUs this process may really use: the affinity mask, cut down to the cgroup CPU quota.
+    OpenMP defaults to every CPU of the host, which stalls badly inside a CPU-limited container."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    try:
+        quota, period = open("/sys/fs/cgroup/cpu.max").read().split()
+        if quota != "max":
+            n = min(n, max(1, int(float(quota) / float(period))))
+    except (OSError, ValueError):
+        try:
+            q = int(open("/sys/fs/cgroup/cpu/cpu.cfs_quota_us").read())
+            per = int(open("/sys/fs/cgroup/cpu/cpu.cfs_period_us").read())
+            if q > 0 and per > 0:
+                n = min(n, max(1, q // per))
+        except (OSError, ValueError):
+            pass
+    return max(1, n)
+
+
 def _load():
     path = os.path.join(_HERE, "liboracle.so")
     if not os.path.exists(path):
         build()
+    os.environ.setdefault("OMP_WAIT_POLICY", "passive")   # idle workers sleep instead of spinning
     return ctypes.CDLL(path)
 
 
@@ -54,6 +74,7 @@ class AdamCfg(ctypes.Structure):
 
 _lib.orc_threads.restype = ctypes.c_int
 _lib.orc_set_threads.argtypes = [ctypes.c_int]
+_lib.orc_set_threads.restype = None
 _lib.orc_decode_n.argtypes = [ctypes.c_int, _p, ctypes.c_size_t, _f, _p]
 _lib.orc_encode_n.argtypes = [ctypes.c_int, _p, ctypes.c_size_t, _p, _f]
 _lib.orc_lane.argtypes = [ctypes.c_uint32] * 3 + [ctypes.c_int] * 2
@@ -68,6 +89,9 @@ _lib.orc_adam.argtypes = [ctypes.POINTER(AdamCfg), ctypes.c_size_t, _p, ctypes.c
 
 def threads():
     return _lib.orc_threads()
+
+
+_lib.orc_set_threads(min(usable_cpus(), 64))
 
 
 def set_threads(n):

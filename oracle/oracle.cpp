@@ -110,6 +110,10 @@ static inline uint8_t enc_fp8(float x) {
   return (uint8_t)(s | (uint32_t)lo);
 }
 
+// max(mx, a) for a statistic that starts at 0: a NaN never replaces mx, Inf does (what fmaxf gives
+// the kernels; spelled as a comparison so that no compiler rewrite can change the NaN behaviour)
+static inline float amax_step(float mx, float a) { return a > mx ? a : mx; }
+
 static inline size_t esize(int t) { return (t == DT_E4M3 || t == DT_E5M2) ? 1 : t == DT_FP32 ? 4 : 2; }
 static inline bool is_fp8(int t) { return t == DT_E4M3 || t == DT_E5M2; }
 
@@ -191,7 +195,7 @@ void orc_cast(int sdt, const void *src, int ddt, void *dst, size_t count, const 
 #pragma omp parallel for schedule(static) reduction(max : mx)
   for (size_t i = 0; i < count; ++i) {
     const float v = hload(sdt, src, i, sinv);
-    mx = fmaxf(mx, fabsf(v));
+    mx = amax_step(mx, fabsf(v));
     hstore(ddt, dst, i, v, qs);
   }
   if (amax && mx > 0.f) *amax = fmaxf(*amax, mx);
@@ -311,7 +315,7 @@ void orc_gemm_cols(const GemmArgs *gp, int order, int j0, int j1) {
           for (int i = 0; i < ib; ++i) o[t][i] = gemv_order_acc(At.data(), g.m, g.k, bc[t], i0 + i);
       }
       for (int t = 0; t < 4 && jj + t < nj; ++t)
-        for (int i = 0; i < ib; ++i) mx = fmaxf(mx, finish(g, i0 + i, j0 + jj + t, o[t][i], csinv, qs));
+        for (int i = 0; i < ib; ++i) mx = amax_step(mx, finish(g, i0 + i, j0 + jj + t, o[t][i], csinv, qs));
     }
   if (g.amax && mx > 0.f) *g.amax = fmaxf(*g.amax, mx);
 }
@@ -373,7 +377,7 @@ void orc_adam(const AdamCfg *cfg, size_t count, void *p_, int pt, const void *g_
     if (cfg->adamw) p = fmaf(-lr_wd, p, p);
     p = fmaf(-cfg->lr, u, p);
     hstore(pt, p_, i, p, 1.f); hstore(mt, m_, i, m, 1.f); hstore(mt, v_, i, v, 1.f);
-    if (q_) { hstore(qt, q_, i, p, qs); mx = fmaxf(mx, fabsf(p)); }
+    if (q_) { hstore(qt, q_, i, p, qs); mx = amax_step(mx, fabsf(p)); }
   }
   if (q_ && amax && mx > 0.f) *amax = fmaxf(*amax, mx);
 }

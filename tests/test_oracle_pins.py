@@ -73,6 +73,16 @@ def test_amax_drops_nan_keeps_inf():
     assert amax == 3.0
     _, amax = orc.cast(np.array([np.nan, -np.inf], np.float32), orc.FP32, orc.BF16, amax=1.0)
     assert np.isinf(amax)
+    # long arrays take the vectorised / multi-threaded loop: same rule there
+    rng = np.random.default_rng(3)
+    bits = rng.integers(0, 2 ** 16, (1 << 20) + 37).astype(np.uint16)
+    for threads in (1, 3):
+        orc.set_threads(threads)
+        assert np.isinf(orc.cast(bits, orc.BF16, orc.E4M3, None, 0.5, amax=0.0)[1])
+        finite = np.where((bits & 0x7F80) == 0x7F80, 0, bits).astype(np.uint16)
+        _, amax = orc.cast(finite, orc.BF16, orc.FP32, amax=0.0)
+        assert amax == np.abs(orc.decode(orc.BF16, finite)).max()
+    orc.set_threads(min(orc.usable_cpus(), 64))
 
 
 def test_gemm_one_mac_equals_lane():
