@@ -1,0 +1,377 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path through the C interface.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One "step" is one pass of the chosen workload (default: c2, the HYBRID dgrad GEMM
+8192 x 4096 x 14336, E5M2 row-wise x E4M3 + BF16 bias -> E5M2 + amax) over synthetic, seeded
+inputs.  One JSON line goes to stdout:
+
+  value      whole-job throughput with the inputs resident in HBM (TFLOP/s for GEMMs, GB/s for
+             the bandwidth-bound workloads), timed with CUDA events on the launching stream over
+             exactly K steps, max over ranks
+  e2e        the same metric with the step's inputs starting in pinned host memory: host-to-device
+             copies, the call through the C interface and the device-to-host read of the result
+             are all inside the timed region
+  roofline   algorithmic FLOPs (or bytes) per launch / average launch time, against the measured
+             peak of MEASURED_PEAKS.json (FP8: twice the measured BF16 figure)
+  cpu_baseline  the CPU oracle (a restatement of the reference's host emulation) on a bounded sample
+             of the same workload, all host threads (rank 0, N = 1 only)
+
+Multi-GPU: launched under torchrun, one rank per GPU.  The GEMM is sharded by column blocks of B
+with A replicated (weak scaling: every rank keeps the full per-GPU problem), the only data-path
+collective is the max-all-reduce of the scalar amax; AdamW / casts shard by parameter chunks,
+the GEMV by weight rows.
+
+--impl reference times the reference's own CPU algorithm (the oracle port: the reference's GPU
+kernels refuse this architecture and its host emulation does not build stand-alone) on the same
+configuration and prints the same line with "impl": "reference".
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/; None where no capture has been taken.
+NCU_TRAFFIC_BYTES = {}
+
+GEMM_LIKE = ("c1", "c2", "c4")
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                 nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                 nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                 nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap"}
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, nm in names.items():
+                    if r & bit:
+                        self.reasons.add(nm)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def cpu_sample(name, target_s=12.0):
+    """The CPU oracle on a bounded sample of workload `name`; returns (value, unit, description)."""
+    import numpy as np
+    import oracle as orc
+    rng = np.random.default_rng(1234)
+    if name in GEMM_LIKE or name.startswith("c3"):
+        shapes = {"c1": (4096, 4096, 4096), "c2": (8192, 4096, 14336), "c4": (4096, 4096, 65536),
+                  "c3n1": (8192, 1, 8192), "c3n8": (8192, 8, 8192)}
+        m, n, k = shapes[name]
+        bt = orc.BF16 if name in ("c4", "c3n1", "c3n8") else (orc.E4M3 if name == "c2" else orc.E5M2)
+        A = rng.integers(0, 120, m * k).astype(np.uint8)
+        # bounded sample: full rows and full k, as many output columns as the MAC budget allows
+        budget = target_s * 1.2e11
+        cols = n if n <= 8 else int(min(n, max(8, budget // (m * k)))) // 4 * 4
+
+        def run(ncols):
+            B = rng.integers(0, 120, ncols * k).astype(np.uint8) if bt != orc.BF16 else \
+                orc.encode(orc.BF16, rng.standard_normal(ncols * k).astype(np.float32))
+            D = np.zeros(m * ncols, np.uint16)
+            t = time.perf_counter()
+            orc.gemm(1, 0, m, ncols, k, 1.0, A, orc.E5M2, k, B, bt, k, 0.0, None, orc.FP32, m, D, orc.BF16, m,
+                     a_sinv=0.125, b_sinv=0.125)
+            return time.perf_counter() - t
+
+        t1 = run(cols)
+        if name.startswith("c3"):
+            return (m * k + 2.0 * k * cols) / t1 / 1e9, "GB/s", f"all {m} rows, {cols} of {n} columns, full k = {k}: {t1:.2f} s"
+        return 2.0 * m * cols * k / t1 / 1e12, "TFLOP/s", f"all {m} rows, {cols} of {n} output columns, full k = {k}: {t1:.2f} s"
+    if name == "c5":
+        cnt = 1 << 26
+        p = orc.encode(orc.BF16, (rng.standard_normal(cnt) * 0.02).astype(np.float32))
+        g = orc.encode(orc.BF16, (rng.standard_normal(cnt) * 1e-3).astype(np.float32))
+        mm, vv, q = np.zeros(cnt, np.uint16), np.zeros(cnt, np.uint16), np.zeros(cnt, np.uint8)
+        cfg = dict(lr=3e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.1, step=1, adamw=1, bias_correction=1, grad_scale=1.0)
+        t = time.perf_counter()
+        orc.adam(cfg, p, orc.BF16, g, orc.BF16, mm, vv, orc.BF16, q, orc.E4M3, 2048.0, 0.0)
+        t1 = time.perf_counter() - t
+        return cnt * 15.0 / t1 / 1e9, "GB/s", f"2^26 of 2^30 parameters: {t1:.2f} s"
+    es = {"cast_f32_e5m2": (orc.FP32, orc.E5M2, 5), "cast_bf16_e4m3": (orc.BF16, orc.E4M3, 3), "cast_e4m3_bf16": (orc.E4M3, orc.BF16, 3)}[name]
+    cnt = 1 << 27
+    src = rng.standard_normal(cnt).astype(np.float32) if es[0] == orc.FP32 else \
+        (rng.integers(0, 120, cnt).astype(np.uint8) if es[0] == orc.E4M3 else rng.integers(0, 2 ** 15, cnt).astype(np.uint16))
+    t = time.perf_counter()
+    orc.cast(src, es[0], es[1], 0.5, 16.0, amax=0.0)
+    t1 = time.perf_counter() - t
+    return cnt * es[2] / t1 / 1e9, "GB/s", f"2^27 elements: {t1:.2f} s"
+
+
+def run_reference(args, metric, unit, config):
+    """The reference's CPU algorithm (oracle port) on this configuration, all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle as orc
+    vals = []
+    t0 = time.perf_counter()
+    for i in range(args.warmup + args.steps):
+        v, u, sample = cpu_sample(args.workload, target_s=4.0)
+        if i >= args.warmup:
+            vals.append(v)
+    val = sum(vals) / len(vals)
+    ms = (time.perf_counter() - t0) * 1e3 / (args.warmup + args.steps)
+    line = {"impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 chain (CPU)", "data": "synthetic", "config": config,
+            "cpu_baseline": {"value": val, "unit": unit, "cores": orc.threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "reference GPU kernels refuse sm_89+ (src/e5m2effma.cuh:22-26); its host emulation is inline in its tests, "
+                    "so the CPU oracle port of that emulation is timed"}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--shrink", type=int, default=1, help="divide the problem sizes (profiler captures)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the timed steps one by one instead of as one CUDA graph")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    name = args.workload
+    is_flops = name in GEMM_LIKE
+    metric = {"c1": "fp8_gemm_4096_e5m2_bf16", "c2": "fp8_hybrid_dgrad_gemm", "c4": "wgrad_e5m2_bf16_fp32_accumulate",
+              "c3n1": "gemv_8192_e5m2_bf16_batch1", "c3n8": "gemv_8192_e5m2_bf16_batch8", "c5": "fused_adamw_bf16_e4m3_copy"}.get(name, name)
+    unit = "TFLOP/s" if is_flops else "GB/s"
+    desc = {"c1": "GEMM M=N=K=4096 E5M2 x E5M2 (TN, scale_inv 0.125) -> BF16",
+            "c2": "HYBRID dgrad GEMM M=8192 N=4096 K=14336, E5M2 row-wise x E4M3 per-tensor + BF16 bias -> E5M2 + amax",
+            "c3n1": "decode GEMV W 8192x8192 E5M2 row-wise, x BF16 batch 1 -> BF16",
+            "c3n8": "decode GEMV W 8192x8192 E5M2 row-wise, x BF16 batch 8 -> BF16",
+            "c4": "wgrad GEMM M=N=4096 K=65536 E5M2 x BF16, beta=1 into FP32 main_grad",
+            "c5": "fused AdamW over 2^30 BF16 parameters, BF16 m/v, E4M3 copy + amax"}.get(name, name)
+    config = {"workload": desc, "per_gpu_problem": "full (weak scaling: column blocks / rows / chunks per rank)",
+              "l2": "inputs larger than L2 (126 MB)" if name not in ("c1", "c3n1", "c3n8") else "rotating input sets larger than L2"}
+    if args.impl == "reference":
+        run_reference(args, metric, unit, config)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from e5m2effma_b200 import capi, workloads
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU (the library has no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- inputs -----------------------------------------------------------------------------------
+    if name == "c2":
+        first = workloads.make("c2_bf16", dev, args.shrink)      # BF16 pass that supplies prev_amax
+        first.launch(torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        prev_amax = float(first.amax.item())
+        if world > 1:
+            t = first.amax.clone()
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            prev_amax = float(t.item())
+        w = first
+        w.d_dtype = capi.E5M2
+        w.D = torch.zeros((w.n, w.m), dtype=torch.uint8, device=dev)
+        workloads.finish_c2(w, prev_amax)
+    else:
+        w = workloads.make(name, dev, args.shrink)
+    stream = torch.cuda.current_stream()
+    sptr = stream.cuda_stream
+
+    # workloads whose operands fit in L2 rotate over input sets that together exceed it
+    rot = None
+    if w.kind == "gemm" and (w.A.numel() * w.A.element_size() + w.B.numel() * w.B.element_size()) < 200e6:
+        sets = int(260e6 // (w.A.numel() * w.A.element_size() + w.B.numel() * w.B.element_size())) + 1
+        rot = [(w.A.clone(), w.B.clone()) for _ in range(sets)]
+
+    def one_pass(i):
+        if rot is not None:
+            a, b = rot[i % len(rot)]
+            w.launch(sptr, a, b)
+        else:
+            w.launch(sptr)
+
+    amax_t = getattr(w, "amax", None)
+
+    def step(i):
+        one_pass(i)
+        if world > 1 and amax_t is not None:
+            dist.all_reduce(amax_t, op=dist.ReduceOp.MAX)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing -------------------------------------------------------------------
+    # The K timed steps are captured once into a CUDA graph and replayed, so that microsecond-scale
+    # kernels (the 4096^3 GEMM, the GEMV) are not timed behind the Python / ctypes launch path.
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    graph = None
+    if not args.no_graph:
+        cs = torch.cuda.Stream()
+        cs.wait_stream(stream)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(cs):
+            sptr_saved, sptr = sptr, cs.cuda_stream
+            with torch.cuda.graph(graph, stream=cs):
+                for i in range(args.steps):
+                    step(i)
+            sptr = sptr_saved
+        graph.replay()          # one untimed replay (also warms the instantiated graph)
+        barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    if graph is not None:
+        graph.replay()
+    else:
+        for i in range(args.steps):
+            step(i)
+    e1.record(stream)
+    barrier()
+    sampler.stop_flag = True
+    sampler.join()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    scale_div = 1e12 if is_flops else 1e9
+    value = w.units * world / (ms_per_step * 1e-3) / scale_div
+    fault = capi.gemm_fault()
+
+    # ---- end to end: pinned host inputs -> device -> call -> result back --------------------------
+    e2e = None
+    if not args.no_e2e:
+        ins, outs = w.io_tensors()
+        outs = [t for t in outs if t is not None]
+        host_in = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in ins]
+        host_out = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
+        h2d = sum(t.numel() * t.element_size() for t in ins)
+        d2h = sum(t.numel() * t.element_size() for t in outs)
+
+        def e2e_step(i):
+            for d, h in zip(ins, host_in):
+                d.copy_(h, non_blocking=True)
+            w.launch(sptr)
+            if world > 1 and amax_t is not None:
+                dist.all_reduce(amax_t, op=dist.ReduceOp.MAX)
+            for h, d in zip(host_out, outs):
+                h.copy_(d, non_blocking=True)
+
+        ksteps = max(3, min(args.steps, 10))
+        for i in range(2):
+            e2e_step(i)
+        barrier()
+        e0.record(stream)
+        for i in range(ksteps):
+            e2e_step(i)
+        e1.record(stream)
+        barrier()
+        ems = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ems], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ems = float(t.item())
+        e2e = {"value": w.units * world / (ems / ksteps * 1e-3) / scale_div, "unit": unit, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": ems / ksteps, "steps": ksteps}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    if is_flops:
+        fp8 = name != "c4"
+        peak = pk["bf16_tflops"] * (2.0 if fp8 else 1.0)
+        roof = {"bound": "tensor", "achieved": w.units / (ms_per_step * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                "peak_source": f"{pk['source']}: " + ("2 x bf16_tflops burst (FP8 issues at twice the BF16 rate)" if fp8 else "bf16_tflops burst"),
+                "nominal_peak": 4500.0 if fp8 else 2250.0}
+    else:
+        roof = {"bound": "hbm", "achieved": w.units / (ms_per_step * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "peak_source": f"{pk['source']}: hbm_gbs (copy)", "nominal_peak": 8000.0}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["frac_of_nominal"] = roof["achieved"] / roof["nominal_peak"]
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(name)
+    roof["algorithmic_units_per_launch"] = w.units
+    roof["kernel_ms"] = ms_per_step
+
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        import oracle as orc
+        v, u, sample = cpu_sample(name)
+        cpu = {"value": v, "unit": u, "cores": orc.threads(), "kind": "port", "sample": sample}
+
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": {"c1": "fp8 (e5m2 x e5m2, f32 accumulate)", "c2": "fp8 (e5m2 x e4m3, f32 accumulate)",
+                      "c4": "bf16 (e5m2 widened exactly, f32 accumulate)"}.get(name, "f32"),
+            "data": "synthetic", "config": config, "clocks": sampler.summary(), "e2e": e2e,
+            "gpu_launches": args.steps * w.launches_per_pass, "timed_as": "cuda_graph" if graph is not None else "stream", "roofline": roof, "cpu_baseline": cpu,
+            "tolerance": "GEMM/GEMV: 1 ulp of the output format + k * 2^-23 * sum|a*b|*|s| (checked by tests/ on every "
+                         "output of the small cases and on sampled rows/columns at full size); casts, AdamW: bit-exact",
+            "gemm_fault": fault}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -4,20 +4,23 @@
 // (include/e5m2effma.h:27-31).
 //
 // Shape of the kernel
-//   * One persistent CTA per SM walks over 128 x BN output tiles (BN = 256 or 128).  Rows of the
-//     tile (index i of D, contiguous in memory) are the M side of the MMA and therefore the 128
-//     lanes of tensor memory; columns j are TMEM columns.
+//   * One persistent CTA per SM walks over output tiles of BI rows (index i, BI = 256 or 128) by
+//     128 columns (index j).  The MMA computes the transposed tile: its M side -- the 128 lanes of
+//     tensor memory -- is j (rows of op(B)^T), its N side -- TMEM columns -- is i.  A thread that
+//     reads its TMEM lane therefore holds consecutive i of one column j, which are contiguous in
+//     the column-major D: the epilogue converts in registers and stores 16 bytes at a time.
 //   * Warp 0 (one elected lane) is the TMA producer: per k-block it brings a 128-row x 128-byte box
-//     of op(A) and a BN-row x 128-byte box of op(B) into a ring of shared-memory stages, both in
+//     of op(B)^T and a BI-row x 128-byte box of op(A) into a ring of shared-memory stages, both in
 //     the 128-byte-swizzled K-major layout the MMA reads.  Rows beyond m / n and bytes beyond k are
 //     zero-filled by TMA, so tails need no special code (k is a multiple of 16 elements, a zero
 //     byte is +0 in every operand format).
 //   * Warp 1 (one elected lane) issues the MMAs: four K = 32-byte steps per stage, accumulating into
 //     one of two TMEM buffers; tcgen05.commit hands the stage back to the producer and, after the
 //     last k-block, the accumulator to the epilogue.
-//   * Warps 2..5 are the epilogue: each owns the TMEM lane quadrant (warp index mod 4), reads 32
-//     columns at a time with tcgen05.ld and applies scale, bias, beta * C, amax and the conversion.
-//     While they drain one buffer the MMA warp already fills the other.
+//   * Warps 2..9 are the epilogue: a warp owns the TMEM lane quadrant (warp index mod 4) and one
+//     half of the tile's i range, reads 32 accumulators of its lane at a time with tcgen05.ld and
+//     applies scale, bias, beta * C, amax and the conversion.  While they drain one buffer the MMA
+//     warp already fills the other.
 //   * FP8 x FP8 (any E5M2 / E4M3 pairing) runs kind::f8f6f4, BF16 x BF16 runs kind::f16; one stage
 //     is 128 bytes of K either way (128 FP8 or 64 BF16 elements), so the two differ only in the
 //     instruction descriptor and the element type of the tensor maps.
@@ -32,20 +35,21 @@
 namespace e5b {
 namespace tc {
 
-constexpr int BM = 128;             // tile rows = MMA M
+constexpr int BM = 128;             // tile columns j = MMA M = TMEM lanes
 constexpr int STAGE_K_BYTES = 128;  // bytes of K per stage = one swizzle row
 constexpr int MMA_K_BYTES = 32;     // bytes of K per tcgen05.mma
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr unsigned long long WAIT_LIMIT = 4000000000ull;  // clock cycles (about two seconds)
 
 __device__ unsigned int g_fault;    // 0 = none; else (role << 24) | detail of the first bounded wait that ran out
 
-template <int BN> struct Cfg {
-  static constexpr int STAGES = BN == 256 ? 4 : 6;
-  static constexpr int A_BYTES = BM * STAGE_K_BYTES;
-  static constexpr int B_BYTES = BN * STAGE_K_BYTES;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int TMEM_COLS = 2 * BN;
+template <int BI> struct Cfg {
+  static constexpr int STAGES = BI == 256 ? 4 : 6;
+  static constexpr int J_BYTES = BM * STAGE_K_BYTES;    // box of op(B)^T: 128 rows j
+  static constexpr int I_BYTES = BI * STAGE_K_BYTES;    // box of op(A): BI rows i
+  static constexpr int STAGE_BYTES = J_BYTES + I_BYTES;
+  static constexpr int TMEM_COLS = 2 * BI;
   // stages + barriers + slack for the 1 KiB alignment of the first stage
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
@@ -159,34 +163,121 @@ __device__ __forceinline__ void store_out(void *d, size_t idx, float v, float qs
   else ((uint8_t *)d)[idx] = (uint8_t)enc_fp8<E5MA_E4M3>(__fmul_rn(v, qs));
 }
 
-// 32 accumulators of row i, columns j0 .. j0+31, through the epilogue.  Per-row terms (sa[i],
-// bias[i]) were read once by the caller; sb[j] is a broadcast load.
-template <int DT>
-__device__ __forceinline__ float drain32(const OutDesc &o, const OutScalars &r, const float acc[32], int i, int j0,
-                                         int n, float row_scale, float bias_i, bool row_ok) {
-  float mx = 0.f;
-  if (!row_ok) return mx;
+// 32 consecutive elements of dtype T (FP32 or BF16) starting at a 16-byte aligned address
+template <int T>
+__device__ __forceinline__ void load32(const void *p, float v[32]) {
+  if (T == E5MA_FP32) {
+    const float4 *q = reinterpret_cast<const float4 *>(p);
 #pragma unroll
-  for (int c = 0; c < 32; ++c) {   // fully unrolled: acc[] stays in registers
-    const int j = j0 + c;
-    if (j >= n) continue;
-    float s = row_scale;
-    if (o.sb_vec) s = __fmul_rn(row_scale, o.sb[j]);
-    float v = __fmul_rn(acc[c], s);
-    if (o.bias) v = __fadd_rn(v, bias_i);
-    if (o.c) v = __fmaf_rn(o.beta, load_elem(o.c_dtype, o.c, (size_t)j * o.ldc + i, r.csinv), v);
-    mx = fmaxf(mx, fabsf(v));
-    store_out<DT>(o.d, (size_t)j * o.ldd + i, v, r.qs);
+    for (int e = 0; e < 8; ++e) { const float4 a = q[e]; v[4 * e] = a.x; v[4 * e + 1] = a.y; v[4 * e + 2] = a.z; v[4 * e + 3] = a.w; }
+  } else {
+    const uint4 *q = reinterpret_cast<const uint4 *>(p);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const uint4 a = q[e];
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int h = 0; h < 4; ++h) { v[8 * e + 2 * h] = __uint_as_float(w[h] << 16); v[8 * e + 2 * h + 1] = __uint_as_float(w[h] & 0xFFFF0000u); }
+    }
+  }
+}
+// 32 consecutive outputs of dtype DT to a 16-byte aligned address
+template <int DT>
+__device__ __forceinline__ void store32(void *p, const float v[32], float qs) {
+  if (DT == E5MA_FP32) {
+    float4 *q = reinterpret_cast<float4 *>(p);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) q[e] = make_float4(v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
+  } else if (DT == E5MA_BF16 || DT == E5MA_FP16) {
+    uint4 *q = reinterpret_cast<uint4 *>(p);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      uint32_t w[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h)
+        w[h] = DT == E5MA_BF16 ? enc_bf16x2(v[8 * e + 2 * h], v[8 * e + 2 * h + 1]) : enc_f16x2(v[8 * e + 2 * h], v[8 * e + 2 * h + 1]);
+      q[e] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  } else {
+    uint4 *q = reinterpret_cast<uint4 *>(p);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      uint32_t w[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const float *x = v + 16 * e + 4 * h;
+        w[h] = enc_fp8x2<DT>(__fmul_rn(x[0], qs), __fmul_rn(x[1], qs)) | (enc_fp8x2<DT>(__fmul_rn(x[2], qs), __fmul_rn(x[3], qs)) << 16);
+      }
+      q[e] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+// What the epilogue of one launch needs beyond OutDesc: whether D (and C) admit 16-byte vector
+// access (base and leading dimension multiples of 16 bytes) and whether bias / C have a dtype the
+// vector path reads directly.
+struct EpiMode { int vec; };
+
+// One thread's 32 accumulators: column j, rows ib .. ib+31.  Fast path when the 32 rows are all
+// inside the matrix and vector access is allowed; otherwise element by element.
+template <int DT>
+__device__ __forceinline__ float drain32(const OutDesc &o, const OutScalars &r, const EpiMode &md, float acc[32],
+                                         int ib, int j, int m, float as_const, float sbj) {
+  float mx = 0.f;
+  if (md.vec && ib + 32 <= m) {
+    if (o.sa_vec) {
+      float sa[32];
+      load32<E5MA_FP32>(o.sa + ib, sa);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) acc[e] = __fmul_rn(acc[e], __fmul_rn(__fmul_rn(o.alpha, sa[e]), sbj));
+    } else {
+      const float s = (o.sa_vec || o.sb_vec) ? __fmul_rn(as_const, sbj) : r.s;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) acc[e] = __fmul_rn(acc[e], s);
+    }
+    if (o.bias) {
+      float b[32];
+      if (o.bias_dtype == E5MA_FP32) load32<E5MA_FP32>((const float *)o.bias + ib, b);
+      else load32<E5MA_BF16>((const uint16_t *)o.bias + ib, b);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) acc[e] = __fadd_rn(acc[e], b[e]);
+    }
+    if (o.c) {
+      float c[32];
+      const size_t off = (size_t)j * o.ldc + ib;
+      if (o.c_dtype == E5MA_FP32) load32<E5MA_FP32>((const float *)o.c + off, c);
+      else load32<E5MA_BF16>((const uint16_t *)o.c + off, c);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) acc[e] = __fmaf_rn(o.beta, c[e], acc[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fabsf(acc[e]));
+    store32<DT>((uint8_t *)o.d + ((size_t)j * o.ldd + ib) * elem_bytes(DT), acc, r.qs);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {   // fully unrolled: acc[] stays in registers
+      const int i = ib + e;
+      if (i < m) {
+        const float a = o.sa_vec ? o.sa[i] : 0.f;
+        const float s = (o.sa_vec || o.sb_vec) ? __fmul_rn(o.sa_vec ? __fmul_rn(o.alpha, a) : as_const, sbj) : r.s;
+        float v = __fmul_rn(acc[e], s);
+        if (o.bias) v = __fadd_rn(v, load_elem(o.bias_dtype, o.bias, (size_t)i, 1.f));
+        if (o.c) v = __fmaf_rn(o.beta, load_elem(o.c_dtype, o.c, (size_t)j * o.ldc + i, r.csinv), v);
+        mx = fmaxf(mx, fabsf(v));
+        store_out<DT>(o.d, (size_t)j * o.ldd + i, v, r.qs);
+      }
+    }
   }
   return mx;
 }
 
 // ---- the kernel ------------------------------------------------------------------------------
-template <int BN, int KIND, int DT>
+// map_i: tensor map of op(A) (rows i, box BI rows); map_j: tensor map of op(B)^T (rows j, box 128 rows).
+template <int BI, int KIND, int DT>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, int m, int n,
-               int k_bytes, uint32_t idesc, OutDesc o) {
-  using C = Cfg<BN>;
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant__ CUtensorMap map_j, int m, int n,
+               int k_bytes, uint32_t idesc, OutDesc o, EpiMode md) {
+  using C = Cfg<BI>;
   extern __shared__ uint8_t smem_raw[];
   // stage ring at the first 1 KiB boundary (the swizzle pattern repeats every 1024 bytes)
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -201,12 +292,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const auto acc_empty = [&](int b) { return bar0 + 8u * (2 * C::STAGES + 2 + b); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (m + BM - 1) / BM, tiles_n = (n + BN - 1) / BN, tiles = tiles_m * tiles_n;
+  const int tiles_i = (m + BI - 1) / BI, tiles_j = (n + BM - 1) / BM, tiles = tiles_i * tiles_j;
   const int kblocks = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -226,18 +317,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int i0 = (t % tiles_m) * BM, j0 = (t / tiles_m) * BN;
+        const int i0 = (t % tiles_i) * BI, j0 = (t / tiles_i) * BM;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)kb)) { ok = false; break; }
           mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-          const uint32_t sa = ring + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
+          const uint32_t sj = ring + s * C::STAGE_BYTES, si = sj + C::J_BYTES;
           // coordinates are in elements of the tensor map: the innermost one counts bytes for FP8 and
           // 2-byte elements for BF16
           const int kc = kb * (KIND == 0 ? STAGE_K_BYTES : STAGE_K_BYTES / 2);
-          tma_load_2d(sa, &map_a, kc, i0, full_bar(s));
-          tma_load_2d(sb, &map_b, kc, j0, full_bar(s));
+          tma_load_2d(sj, &map_j, kc, j0, full_bar(s));
+          tma_load_2d(si, &map_i, kc, i0, full_bar(s));
         }
       }
     }
@@ -250,18 +341,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t buf = lt & 1u, use = lt >> 1;
         if (!mbar_wait(acc_empty(buf), (use & 1u) ^ 1u, abort_flag, (2u << 24) | 0xFFFFu)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BN;
+        const uint32_t d_tmem = tmem_base + buf * BI;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1u;
           if (!mbar_wait(full_bar(s), ph, abort_flag, (2u << 24) | (uint32_t)kb)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = ring + s * C::STAGE_BYTES, sb = sa + C::A_BYTES;
-          const uint64_t da = kmajor_sw128_desc(sa), db = kmajor_sw128_desc(sb);
+          const uint32_t sj = ring + s * C::STAGE_BYTES, si = sj + C::J_BYTES;
+          const uint64_t dj = kmajor_sw128_desc(sj), di = kmajor_sw128_desc(si);
 #pragma unroll
           for (int ks = 0; ks < STAGE_K_BYTES / MMA_K_BYTES; ++ks) {
             // stepping 32 bytes along K inside the swizzled row = +2 in the 16-byte address field
-            mma_ss<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, idesc, (kb | ks) != 0);
+            mma_ss<KIND>(d_tmem, dj + 2u * ks, di + 2u * ks, idesc, (kb | ks) != 0);
           }
           mma_commit(empty_bar(s));
         }
@@ -269,33 +360,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else {
-    // ---------------- epilogue warps 2..5: TMEM lane quadrant = warp % 4 ----------------
-    const int quad = warp & 3;
+    // ------------- epilogue warps: TMEM lane quadrant = warp % 4, half of the i range = (warp - 2) / 4 -------------
+    const int quad = warp & 3, half = (warp - 2) >> 2;
     const OutScalars r = out_begin(o);
+    const float as_const = __fmul_rn(o.alpha, o.sa_vec ? 1.f : ld_or_one(o.sa));
+    const float sb_const = o.sb_vec ? 1.f : ld_or_one(o.sb);
     float mx = 0.f;
     uint32_t lt = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++lt) {
-      const int i0 = (t % tiles_m) * BM, j0 = (t / tiles_m) * BN;
+      const int i0 = (t % tiles_i) * BI, j0 = (t / tiles_i) * BM;
       const uint32_t buf = lt & 1u, use = lt >> 1;
-      ok = mbar_wait(acc_full(buf), use & 1u, abort_flag, (3u << 24) | (uint32_t)quad);
+      ok = mbar_wait(acc_full(buf), use & 1u, abort_flag, (3u << 24) | (uint32_t)warp);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int i = i0 + quad * 32 + lane;
-      const bool row_ok = i < m;
-      float row_scale = r.s, bias_i = 0.f;
-      if (row_ok) {
-        if (o.sa_vec || o.sb_vec) row_scale = __fmul_rn(o.alpha, o.sa_vec ? o.sa[i] : ld_or_one(o.sa));
-        if (o.sa_vec && !o.sb_vec) row_scale = __fmul_rn(row_scale, ld_or_one(o.sb));
-        if (o.bias) bias_i = load_elem(o.bias_dtype, o.bias, (size_t)i, 1.f);
-      }
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (j0 + c0 >= n) break;   // warp-uniform
+      const int j = j0 + quad * 32 + lane;
+      const bool col_ok = j < n;
+      const float sbj = col_ok && o.sb_vec ? o.sb[j] : sb_const;
+      const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BI;
+      for (int c0 = half * (BI / 2); c0 < (half + 1) * (BI / 2); c0 += 32) {
+        if (i0 + c0 >= m) break;   // warp-uniform
         float acc[32];
-        tmem_ld32(t_row + c0, acc);
-        mx = fmaxf(mx, drain32<DT>(o, r, acc, i, j0 + c0, n, row_scale, bias_i, row_ok));
+        tmem_ld32(t_lane + c0, acc);
+        if (col_ok) mx = fmaxf(mx, drain32<DT>(o, r, md, acc, i0 + c0, j, m, as_const, sbj));
       }
       tc_fence_before();
       __syncwarp();
@@ -354,41 +442,42 @@ static bool make_map(CUtensorMap *map, const void *base, int elem_bytes, int k, 
          CUDA_SUCCESS;
 }
 
-template <int BN, int KIND, int DT>
-static cudaError_t launch_cfg(const CUtensorMap &ma, const CUtensorMap &mb, int m, int n, int k_bytes, uint32_t idesc,
-                              const OutDesc &o, int sms, cudaStream_t s) {
-  using C = Cfg<BN>;
+template <int BI, int KIND, int DT>
+static cudaError_t launch_cfg(const CUtensorMap &mi, const CUtensorMap &mj, int m, int n, int k_bytes, uint32_t idesc,
+                              const OutDesc &o, const EpiMode &md, int sms, cudaStream_t s) {
+  using C = Cfg<BI>;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, KIND, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BI, KIND, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     attr_done[dev & 63] = true;
   }
-  const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  const int tiles = ((m + BI - 1) / BI) * ((n + BM - 1) / BM);
   const int grid = tiles < sms ? tiles : sms;
-  gemm_tc_kernel<BN, KIND, DT><<<grid, THREADS, C::SMEM_BYTES, s>>>(ma, mb, m, n, k_bytes, idesc, o);
+  gemm_tc_kernel<BI, KIND, DT><<<grid, THREADS, C::SMEM_BYTES, s>>>(mi, mj, m, n, k_bytes, idesc, o, md);
   return cudaGetLastError();
 }
 
-template <int BN, int KIND>
-static cudaError_t launch_dt(const CUtensorMap &ma, const CUtensorMap &mb, int m, int n, int k_bytes, uint32_t idesc,
-                             const OutDesc &o, int sms, cudaStream_t s) {
+template <int BI, int KIND>
+static cudaError_t launch_dt(const CUtensorMap &mi, const CUtensorMap &mj, int m, int n, int k_bytes, uint32_t idesc,
+                             const OutDesc &o, const EpiMode &md, int sms, cudaStream_t s) {
   switch (o.d_dtype) {
-    case E5MA_BF16: return launch_cfg<BN, KIND, E5MA_BF16>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
-    case E5MA_FP32: return launch_cfg<BN, KIND, E5MA_FP32>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
-    case E5MA_FP16: return launch_cfg<BN, KIND, E5MA_FP16>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
-    case E5MA_E5M2: return launch_cfg<BN, KIND, E5MA_E5M2>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
-    default: return launch_cfg<BN, KIND, E5MA_E4M3>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
+    case E5MA_BF16: return launch_cfg<BI, KIND, E5MA_BF16>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
+    case E5MA_FP32: return launch_cfg<BI, KIND, E5MA_FP32>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
+    case E5MA_FP16: return launch_cfg<BI, KIND, E5MA_FP16>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
+    case E5MA_E5M2: return launch_cfg<BI, KIND, E5MA_E5M2>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
+    default: return launch_cfg<BI, KIND, E5MA_E4M3>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
   }
 }
 
 }  // namespace tc
 
 // Blackwell tile selection (takes the place of the reference's tuned per-architecture tables,
-// src/e5m2effma_tuned.h): 128 x 256 tiles when they fill the machine or n is wide, else 128 x 128.
+// src/e5m2effma_tuned.h): tiles of 256 rows x 128 columns when they fill the machine or m is large,
+// else 128 x 128.
 cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const uint8_t *A, int lda,
                            const uint8_t *B, int ldb, int m, int n, int k, const OutDesc &o, int sms,
                            cudaStream_t s) {
@@ -398,18 +487,28 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   const bool bf = a_dtype == E5MA_BF16 && b_dtype == E5MA_BF16;
   if (!f8 && !bf) return cudaErrorNotSupported;
   const int eb = f8 ? 1 : 2;
-  const int tiles256 = ((m + BM - 1) / BM) * ((n + 255) / 256);
-  const bool wide = n > 128 && (tiles256 >= sms || n % 256 == 0 || n > 1024);
-  const int bn = wide ? 256 : 128;
-  CUtensorMap ma, mb;
-  if (!make_map(&ma, A, eb, k, m, lda, BM) || !make_map(&mb, B, eb, k, n, ldb, bn)) return cudaErrorNotSupported;
-  const int fa = f8 ? (a_dtype == E5MA_E5M2 ? 1 : 0) : 1, fb = f8 ? (b_dtype == E5MA_E5M2 ? 1 : 0) : 1;
-  const uint32_t idesc = instr_desc(fa, fb, BM, bn);
+  const int tiles256 = ((m + 255) / 256) * ((n + BM - 1) / BM);
+  const bool wide = m > 128 && (tiles256 >= sms || m % 256 == 0 || m > 1024);
+  const int bi = wide ? 256 : 128;
+  CUtensorMap mi, mj;
+  if (!make_map(&mi, A, eb, k, m, lda, bi) || !make_map(&mj, B, eb, k, n, ldb, BM)) return cudaErrorNotSupported;
+  // the MMA's A operand (M side) is op(B)^T, its B operand (N side) is op(A)
+  const int fi = f8 ? (a_dtype == E5MA_E5M2 ? 1 : 0) : 1, fj = f8 ? (b_dtype == E5MA_E5M2 ? 1 : 0) : 1;
+  const uint32_t idesc = instr_desc(fj, fi, BM, bi);
   const int k_bytes = k * eb;
-  if (f8) return wide ? launch_dt<256, 0>(ma, mb, m, n, k_bytes, idesc, o, sms, s)
-                      : launch_dt<128, 0>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
-  return wide ? launch_dt<256, 1>(ma, mb, m, n, k_bytes, idesc, o, sms, s)
-              : launch_dt<128, 1>(ma, mb, m, n, k_bytes, idesc, o, sms, s);
+  // 16-byte vector access in the epilogue: D (and C, bias) bases and column pitches must allow it
+  const auto vec_ok = [](const void *p, int ld, int dtype) {
+    return ((uintptr_t)p & 15u) == 0 && ((size_t)ld * elem_bytes(dtype)) % 16 == 0;
+  };
+  EpiMode md;
+  md.vec = vec_ok(o.d, o.ldd, o.d_dtype);
+  if (o.c && !((o.c_dtype == E5MA_FP32 || o.c_dtype == E5MA_BF16) && vec_ok(o.c, o.ldc, o.c_dtype))) md.vec = 0;
+  if (o.bias && !((o.bias_dtype == E5MA_FP32 || o.bias_dtype == E5MA_BF16) && ((uintptr_t)o.bias & 15u) == 0)) md.vec = 0;
+  if (o.sa_vec && ((uintptr_t)o.sa & 15u)) md.vec = 0;
+  if (f8) return wide ? launch_dt<256, 0>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s)
+                      : launch_dt<128, 0>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
+  return wide ? launch_dt<256, 1>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s)
+              : launch_dt<128, 1>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
 }
 
 }  // namespace e5b

@@ -86,10 +86,11 @@ static inline uint16_t enc_f16(float v) {
 // or beyond the largest finite magnitude (Inf too) saturate, NaN -> 0x7F without a sign.  Written
 // as a search over the midpoints of neighbouring codes so that it shares nothing with the
 // bit-twiddling encoders it is used to check.
-static float g_mid4[126], g_mid5[123];
+static float g_mid4[126], g_mid5[123], g_lut4[256], g_lut5[256];   // midpoints; decoded value of every code
 static bool g_tables = false;
 static void build_tables() {
   if (g_tables) return;
+  for (int c = 0; c < 256; ++c) { g_lut4[c] = dec_e4m3((uint8_t)c); g_lut5[c] = dec_e5m2((uint8_t)c); }
   for (int c = 0; c < 126; ++c) g_mid4[c] = 0.5f * (dec_e4m3((uint8_t)c) + dec_e4m3((uint8_t)(c + 1)));
   for (int c = 0; c < 123; ++c) g_mid5[c] = 0.5f * (dec_e5m2((uint8_t)c) + dec_e5m2((uint8_t)(c + 1)));
   g_tables = true;
@@ -214,44 +215,53 @@ struct GemmArgs {
 };
 
 // op(A) decoded to FP32 as At[kk * m + i]; op(B) as Bt[j * k + kk]  (raw values, scale 1)
+// raw operand element (scale 1); FP8 through the table of decoded codes (same values as dec_*)
+static inline float operand_value(int t, const void *p, size_t i) {
+  if (t == DT_E4M3) return g_lut4[((const uint8_t *)p)[i]];
+  if (t == DT_E5M2) return g_lut5[((const uint8_t *)p)[i]];
+  return hload(t, p, i, 1.f);
+}
 static void decode_operands(const GemmArgs &g, std::vector<float> &At, std::vector<float> &Bt, int j0, int j1) {
+  build_tables();
   const bool a_kc = g.transa == 1, b_kc = g.transb == 0;
   At.resize((size_t)g.k * g.m);
+  if (a_kc) {   // walk the storage rows (K contiguous), 16 x 16 blocks keep both sides in cache lines
 #pragma omp parallel for schedule(static)
-  for (int kk = 0; kk < g.k; ++kk)
-    for (int i = 0; i < g.m; ++i)
-      At[(size_t)kk * g.m + i] = hload(g.a_dtype, g.a, a_kc ? (size_t)i * g.lda + kk : (size_t)kk * g.lda + i, 1.f);
+    for (int ib = 0; ib < g.m; ib += 16)
+      for (int kb = 0; kb < g.k; kb += 16)
+        for (int i = ib; i < std::min(g.m, ib + 16); ++i)
+          for (int kk = kb; kk < std::min(g.k, kb + 16); ++kk)
+            At[(size_t)kk * g.m + i] = operand_value(g.a_dtype, g.a, (size_t)i * g.lda + kk);
+  } else {
+#pragma omp parallel for schedule(static)
+    for (int kk = 0; kk < g.k; ++kk)
+      for (int i = 0; i < g.m; ++i) At[(size_t)kk * g.m + i] = operand_value(g.a_dtype, g.a, (size_t)kk * g.lda + i);
+  }
   Bt.resize((size_t)g.k * (j1 - j0));
 #pragma omp parallel for schedule(static)
   for (int j = j0; j < j1; ++j)
     for (int kk = 0; kk < g.k; ++kk)
-      Bt[(size_t)(j - j0) * g.k + kk] = hload(g.b_dtype, g.b, b_kc ? (size_t)j * g.ldb + kk : (size_t)kk * g.ldb + j, 1.f);
+      Bt[(size_t)(j - j0) * g.k + kk] = operand_value(g.b_dtype, g.b, b_kc ? (size_t)j * g.ldb + kk : (size_t)kk * g.ldb + j);
 }
 
-// acc[jj][i] = chain over ascending kk of fmaf(A[i,kk], B[kk,j], acc), for IB rows x 4 columns.
-// Each output keeps its own ascending-k order; the blocking only reuses loads.
-CLONES static void chain_block(const float *At, int m, int k, const float *b0, const float *b1, const float *b2,
-                               const float *b3, int i0, int ib, float *o0, float *o1, float *o2, float *o3) {
+// Ascending-k FMA chains for a 64-row x 4-column block over k-steps [k0, k1), continuing from and
+// writing back to the accumulators acc0..acc3 (64 floats each).  Splitting k into blocks and
+// parking the partial sums in memory in between does not change any output's operation order.
+// ap: packed op(A) rows of this block, ap[kk * 64 + r].
+CLONES static void chain_block(const float *ap, int k0, int k1, const float *b0, const float *b1, const float *b2,
+                               const float *b3, float *acc0, float *acc1, float *acc2, float *acc3) {
   float a0[64], a1[64], a2[64], a3[64];
-  for (int i = 0; i < 64; ++i) a0[i] = a1[i] = a2[i] = a3[i] = 0.f;
-  for (int kk = 0; kk < k; ++kk) {
-    const float *ar = At + (size_t)kk * m + i0;
+  for (int i = 0; i < 64; ++i) { a0[i] = acc0[i]; a1[i] = acc1[i]; a2[i] = acc2[i]; a3[i] = acc3[i]; }
+  for (int kk = k0; kk < k1; ++kk) {
+    const float *ar = ap + (size_t)kk * 64;
     const float x0 = b0[kk], x1 = b1[kk], x2 = b2[kk], x3 = b3[kk];
-    if (ib == 64) {
-      for (int i = 0; i < 64; ++i) {
-        const float av = ar[i];
-        a0[i] = fmaf(av, x0, a0[i]); a1[i] = fmaf(av, x1, a1[i]);
-        a2[i] = fmaf(av, x2, a2[i]); a3[i] = fmaf(av, x3, a3[i]);
-      }
-    } else {
-      for (int i = 0; i < ib; ++i) {
-        const float av = ar[i];
-        a0[i] = fmaf(av, x0, a0[i]); a1[i] = fmaf(av, x1, a1[i]);
-        a2[i] = fmaf(av, x2, a2[i]); a3[i] = fmaf(av, x3, a3[i]);
-      }
+    for (int i = 0; i < 64; ++i) {
+      const float av = ar[i];
+      a0[i] = fmaf(av, x0, a0[i]); a1[i] = fmaf(av, x1, a1[i]);
+      a2[i] = fmaf(av, x2, a2[i]); a3[i] = fmaf(av, x3, a3[i]);
     }
   }
-  for (int i = 0; i < ib; ++i) { o0[i] = a0[i]; o1[i] = a1[i]; o2[i] = a2[i]; o3[i] = a3[i]; }
+  for (int i = 0; i < 64; ++i) { acc0[i] = a0[i]; acc1[i] = a1[i]; acc2[i] = a2[i]; acc3[i] = a3[i]; }
 }
 
 // The GEMV kernel of the reference sums in another order: lane l takes k = 256c + 8l + j
@@ -299,24 +309,39 @@ void orc_gemm_cols(const GemmArgs *gp, int order, int j0, int j1) {
   const float csinv = g.c && is_fp8(g.c_dtype) && g.c_sinv ? *g.c_sinv : 1.f;
   const float qs = is_fp8(g.d_dtype) && g.d_scale ? *g.d_scale : 1.f;
   float mx = 0.f;
-  const int nj = j1 - j0, njb = (nj + 3) / 4, nib = (g.m + 63) / 64;
-  std::vector<float> zero((size_t)std::max(g.k, 1), 0.f);
-#pragma omp parallel for schedule(dynamic, 1) collapse(2) reduction(max : mx)
-  for (int ibk = 0; ibk < nib; ++ibk)
-    for (int jb = 0; jb < njb; ++jb) {
-      const int i0 = ibk * 64, ib = std::min(64, g.m - i0), jj = jb * 4;
-      float o[4][64];
-      const float *bc[4];
-      for (int t = 0; t < 4; ++t) bc[t] = jj + t < nj ? Bt.data() + (size_t)(jj + t) * g.k : zero.data();
+  const int nj = j1 - j0, njp = (nj + 3) / 4 * 4, nib = (g.m + 63) / 64;
+  const int KB = 256;   // k-block: 64 rows x 256 k of packed A (64 KiB) stay cache-resident over all columns
+#pragma omp parallel reduction(max : mx)
+  {
+    std::vector<float> ap((size_t)64 * std::max(g.k, 1)), acc((size_t)njp * 64), zero((size_t)std::max(g.k, 1), 0.f);
+#pragma omp for schedule(dynamic, 1)
+    for (int ibk = 0; ibk < nib; ++ibk) {
+      const int i0 = ibk * 64, ib = std::min(64, g.m - i0);
       if (order == 0) {
-        chain_block(At.data(), g.m, g.k, bc[0], bc[1], bc[2], bc[3], i0, ib, o[0], o[1], o[2], o[3]);
+        for (int kk = 0; kk < g.k; ++kk) {
+          const float *src = At.data() + (size_t)kk * g.m + i0;
+          float *dst = ap.data() + (size_t)kk * 64;
+          for (int r = 0; r < 64; ++r) dst[r] = r < ib ? src[r] : 0.f;
+        }
+        std::fill(acc.begin(), acc.end(), 0.f);
+        for (int k0 = 0; k0 < g.k; k0 += KB) {
+          const int k1 = std::min(g.k, k0 + KB);
+          for (int jj = 0; jj < njp; jj += 4) {
+            const float *bc[4];
+            for (int t = 0; t < 4; ++t) bc[t] = jj + t < nj ? Bt.data() + (size_t)(jj + t) * g.k : zero.data();
+            float *a = acc.data() + (size_t)jj * 64;
+            chain_block(ap.data(), k0, k1, bc[0], bc[1], bc[2], bc[3], a, a + 64, a + 128, a + 192);
+          }
+        }
       } else {
-        for (int t = 0; t < 4 && jj + t < nj; ++t)
-          for (int i = 0; i < ib; ++i) o[t][i] = gemv_order_acc(At.data(), g.m, g.k, bc[t], i0 + i);
+        for (int jj = 0; jj < nj; ++jj)
+          for (int i = 0; i < ib; ++i)
+            acc[(size_t)jj * 64 + i] = gemv_order_acc(At.data(), g.m, g.k, Bt.data() + (size_t)jj * g.k, i0 + i);
       }
-      for (int t = 0; t < 4 && jj + t < nj; ++t)
-        for (int i = 0; i < ib; ++i) mx = amax_step(mx, finish(g, i0 + i, j0 + jj + t, o[t][i], csinv, qs));
+      for (int jj = 0; jj < nj; ++jj)
+        for (int i = 0; i < ib; ++i) mx = amax_step(mx, finish(g, i0 + i, j0 + jj, acc[(size_t)jj * 64 + i], csinv, qs));
     }
+  }
   if (g.amax && mx > 0.f) *g.amax = fmaxf(*g.amax, mx);
 }
 void orc_gemm(const GemmArgs *g, int order) { orc_gemm_cols(g, order, 0, g->n); }
