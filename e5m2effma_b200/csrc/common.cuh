@@ -45,6 +45,32 @@ __device__ __forceinline__ void dec_fp8x4(uint32_t w, float v[4]) {
   v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
 
+// ---- FP8 -> BF16 widening (tensor-core operands) ------------------------------------------------
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// Four FP8 codes (bytes 0..3 of w, ascending k) -> BF16 pairs (k0,k1) and (k2,k3).
+// The 7 magnitude bits of a code, placed so that its exponent field lands in the BF16 exponent
+// field, are the BF16 encoding of value * 2^-112 (E5M2, bias 15 -> 127) or value * 2^-120 (E4M3,
+// bias 7 -> 127), subnormal codes included; one BF16 multiply by the power of two restores the value.
+template <int T>
+__device__ __forceinline__ void fp8x4_to_bf16x2(uint32_t w, uint32_t &lo, uint32_t &hi) {
+  const uint32_t p0 = __byte_perm(w, 0, 0x1404);   // (b1 << 24) | (b0 << 8)
+  const uint32_t p1 = __byte_perm(w, 0, 0x3424);   // (b3 << 24) | (b2 << 8)
+  if (T == E5MA_E5M2) {
+    const uint32_t k = 0x77807780u;                // 2^112 in both halves
+    lo = mul_bf16x2((p0 & 0x80008000u) | ((p0 >> 3) & 0x0FE00FE0u), k);
+    hi = mul_bf16x2((p1 & 0x80008000u) | ((p1 >> 3) & 0x0FE00FE0u), k);
+  } else {
+    const uint32_t k = 0x7B807B80u;                // 2^120 in both halves
+    lo = mul_bf16x2((p0 & 0x80008000u) | ((p0 >> 4) & 0x07F007F0u), k);
+    hi = mul_bf16x2((p1 & 0x80008000u) | ((p1 >> 4) & 0x07F007F0u), k);
+  }
+}
+
 // ---- encode --------------------------------------------------------------------------------
 __device__ __forceinline__ bool is_nan(float x) { return (__float_as_uint(x) & 0x7FFFFFFFu) > 0x7F800000u; }
 

@@ -123,7 +123,21 @@ __global__ void __launch_bounds__(256) cast_kernel(const void *__restrict__ src,
   float mx = 0.f;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (size_t)gridDim.x * blockDim.x;
   const size_t groups = VEC ? count / 16 : 0;
-  for (size_t gidx = tid; gidx < groups; gidx += nthr) {
+  // G groups per step so that every thread keeps 64 bytes of loads in flight whatever the source width
+  constexpr int G = 4 / elem_bytes(TS);
+  size_t gidx = tid;
+  for (; gidx + (G - 1) * nthr < groups; gidx += G * nthr) {
+    float v[G][16];
+#pragma unroll
+    for (int u = 0; u < G; ++u) load16<TS>(src, (gidx + u * nthr) * 16, sinv, v[u]);
+#pragma unroll
+    for (int u = 0; u < G; ++u) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) mx = fmaxf(mx, fabsf(v[u][e]));
+      store16<TD>(dst, (gidx + u * nthr) * 16, qs, v[u]);
+    }
+  }
+  for (; gidx < groups; gidx += nthr) {
     float v[16];
     load16<TS>(src, gidx * 16, sinv, v);
 #pragma unroll

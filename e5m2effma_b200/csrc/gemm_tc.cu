@@ -24,12 +24,17 @@
 //   * FP8 x FP8 (any E5M2 / E4M3 pairing) runs kind::f8f6f4, BF16 x BF16 runs kind::f16; one stage
 //     is 128 bytes of K either way (128 FP8 or 64 BF16 elements), so the two differ only in the
 //     instruction descriptor and the element type of the tensor maps.
+//   * FP8 x BF16 pairs (either order) also run kind::f16: products must stay exact, so the FP8
+//     operand is widened to BF16, which is exact (at most 4 significant bits).  TMA brings its raw
+//     bytes (64 per row and k-block) into the stage; four converter warps (10..13) rewrite them as
+//     BF16 in the swizzled K-major layout, fence towards the async proxy and signal the MMA warp.
 //   * No cluster features are used: every CTA loads its own operand boxes.
 //
 // Every wait on an mbarrier is bounded.  A wait that runs out records a fault word, raises a
 // block-wide abort flag that every role polls, and the CTA leaves through the common exit, where
 // tensor memory is released.  e5b_gemm_fault() reads the word back.
 #include <cuda.h>
+#include <stdlib.h>
 #include "common.cuh"
 
 namespace e5b {
@@ -39,19 +44,26 @@ constexpr int BM = 128;             // tile columns j = MMA M = TMEM lanes
 constexpr int STAGE_K_BYTES = 128;  // bytes of K per stage = one swizzle row
 constexpr int MMA_K_BYTES = 32;     // bytes of K per tcgen05.mma
 constexpr int EPI_WARPS = 8;
-constexpr int THREADS = 64 + 32 * EPI_WARPS;
+constexpr int CONV_WARPS = 4;
+constexpr int THREADS = 64 + 32 * EPI_WARPS;             // producer, MMA, epilogue
+constexpr int THREADS_CONV = THREADS + 32 * CONV_WARPS;  // ... plus the FP8 -> BF16 converter warps
 constexpr unsigned long long WAIT_LIMIT = 4000000000ull;  // clock cycles (about two seconds)
 
 __device__ unsigned int g_fault;    // 0 = none; else (role << 24) | detail of the first bounded wait that ran out
 
-template <int BI> struct Cfg {
-  static constexpr int STAGES = BI == 256 ? 4 : 6;
+// CONV: 0 both operands arrive ready for the MMA; 1 the i-side operand (op(A)) is FP8 and is
+// widened to BF16 in shared memory; 2 the j-side operand (op(B)) is.
+template <int BI, int CONV> struct Cfg {
   static constexpr int J_BYTES = BM * STAGE_K_BYTES;    // box of op(B)^T: 128 rows j
   static constexpr int I_BYTES = BI * STAGE_K_BYTES;    // box of op(A): BI rows i
-  static constexpr int STAGE_BYTES = J_BYTES + I_BYTES;
+  static constexpr int RAW_ROWS = CONV == 1 ? BI : (CONV == 2 ? BM : 0);
+  static constexpr int RAW_BYTES = RAW_ROWS * (STAGE_K_BYTES / 2);   // 64 FP8 bytes per row and k-block
+  static constexpr int STAGE_BYTES = J_BYTES + I_BYTES + RAW_BYTES;
+  static constexpr int STAGES = CONV ? (BI == 256 ? 3 : 4) : (BI == 256 ? 4 : 6);
+  static constexpr int NTHREADS = CONV ? THREADS_CONV : THREADS;
   static constexpr int TMEM_COLS = 2 * BI;
   // stages + barriers + slack for the 1 KiB alignment of the first stage
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 384;
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -216,7 +228,7 @@ __device__ __forceinline__ void store32(void *p, const float v[32], float qs) {
 // What the epilogue of one launch needs beyond OutDesc: whether D (and C) admit 16-byte vector
 // access (base and leading dimension multiples of 16 bytes) and whether bias / C have a dtype the
 // vector path reads directly.
-struct EpiMode { int vec; };
+struct EpiMode { int vec; int split; };   // split: the last partial wave of tiles is cut into half tiles
 
 // One thread's 32 accumulators: column j, rows ib .. ib+31.  Fast path when the 32 rows are all
 // inside the matrix and vector access is allowed; otherwise element by element.
@@ -273,30 +285,49 @@ __device__ __forceinline__ float drain32(const OutDesc &o, const OutScalars &r, 
 
 // ---- the kernel ------------------------------------------------------------------------------
 // map_i: tensor map of op(A) (rows i, box BI rows); map_j: tensor map of op(B)^T (rows j, box 128 rows).
-template <int BI, int KIND, int DT>
-__global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant__ CUtensorMap map_j, int m, int n,
-               int k_bytes, uint32_t idesc, OutDesc o, EpiMode md) {
-  using C = Cfg<BI>;
+// With CONV the map of the FP8 operand has 64-byte unswizzled boxes and lands in the raw area.
+// FT: dtype of the FP8 operand that is widened (CONV != 0).
+template <int BI, int KIND, int DT, int CONV, int FT>
+__global__ void __launch_bounds__(Cfg<BI, CONV>::NTHREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant__ CUtensorMap map_j,
+               const __grid_constant__ CUtensorMap map_ih, int m, int n, int k_bytes, uint32_t idesc, uint32_t idesc_half,
+               OutDesc o, EpiMode md) {
+  using C = Cfg<BI, CONV>;
   extern __shared__ uint8_t smem_raw[];
   // stage ring at the first 1 KiB boundary (the swizzle pattern repeats every 1024 bytes)
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *after_ring = smem_raw + (ring - smem_u32(smem_raw)) + C::STAGES * C::STAGE_BYTES;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(after_ring);            // full[S], empty[S], acc_full[2], acc_empty[2]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + 4);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(after_ring);   // full[S], empty[S], acc_full[2], acc_empty[2], ready[S]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * C::STAGES + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   const auto full_bar = [&](int s) { return bar0 + 8u * s; };
   const auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
   const auto acc_full = [&](int b) { return bar0 + 8u * (2 * C::STAGES + b); };
   const auto acc_empty = [&](int b) { return bar0 + 8u * (2 * C::STAGES + 2 + b); };
+  const auto ready_bar = [&](int s) { return bar0 + 8u * (2 * C::STAGES + 4 + s); };   // converted operand in place
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_i = (m + BI - 1) / BI, tiles_j = (n + BM - 1) / BM, tiles = tiles_i * tiles_j;
   const int kblocks = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
 
+  // Work items.  Normally one item = one tile, dealt round-robin to the CTAs.  When the last round would
+  // keep at most half of the CTAs busy, its tiles are cut into two half tiles (BI / 2 rows: map_ih boxes,
+  // idesc_half) so that the round takes half as long.  Every role derives the same list from this.
+  const int grid_n = gridDim.x;
+  const int full_items = (tiles / grid_n) * grid_n, rem = tiles - full_items;
+  const bool split = CONV == 0 && md.split && rem > 0 && 2 * rem <= grid_n;
+  const int items = split ? full_items + 2 * rem : tiles;
+  const auto item_at = [&](int item, int &i0, int &j0, int &rows) {
+    int tile = item, hf = 0;
+    rows = BI;
+    if (split && item >= full_items) { const int h = item - full_items; tile = full_items + (h >> 1); hf = h & 1; rows = BI / 2; }
+    i0 = (tile % tiles_i) * BI + hf * (BI / 2);
+    j0 = (tile / tiles_i) * BM;
+  };
+
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); mbar_init(ready_bar(s), CONV_WARPS); }
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -316,19 +347,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int i0 = (t % tiles_i) * BI, j0 = (t / tiles_i) * BM;
+      for (int t = blockIdx.x; t < items && ok; t += gridDim.x) {
+        int i0, j0, rows;
+        item_at(t, i0, j0, rows);
+        const bool half_tile = rows != BI;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)kb)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-          const uint32_t sj = ring + s * C::STAGE_BYTES, si = sj + C::J_BYTES;
+          mbar_expect_tx(full_bar(s), C::J_BYTES + (half_tile ? C::I_BYTES / 2 : C::I_BYTES) + C::RAW_BYTES -
+                                          (CONV == 1 ? C::I_BYTES : (CONV == 2 ? C::J_BYTES : 0)));
+          const uint32_t sj = ring + s * C::STAGE_BYTES, si = sj + C::J_BYTES, sraw = si + C::I_BYTES;
           // coordinates are in elements of the tensor map: the innermost one counts bytes for FP8 and
-          // 2-byte elements for BF16
+          // 2-byte elements for BF16; a k-block is 128 FP8 or 64 BF16 (and then also 64 raw FP8) elements
           const int kc = kb * (KIND == 0 ? STAGE_K_BYTES : STAGE_K_BYTES / 2);
-          tma_load_2d(sj, &map_j, kc, j0, full_bar(s));
-          tma_load_2d(si, &map_i, kc, i0, full_bar(s));
+          tma_load_2d(CONV == 2 ? sraw : sj, &map_j, kc, j0, full_bar(s));
+          tma_load_2d(CONV == 1 ? sraw : si, half_tile ? &map_ih : &map_i, kc, i0, full_bar(s));
         }
       }
     }
@@ -337,7 +371,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0, lt = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++lt) {
+      for (int t = blockIdx.x; t < items && ok; t += gridDim.x, ++lt) {
+        int i0, j0, rows;
+        item_at(t, i0, j0, rows);
+        const uint32_t idesc_t = rows != BI ? idesc_half : idesc;
         const uint32_t buf = lt & 1u, use = lt >> 1;
         if (!mbar_wait(acc_empty(buf), (use & 1u) ^ 1u, abort_flag, (2u << 24) | 0xFFFFu)) { ok = false; break; }
         tc_fence_after();
@@ -346,17 +383,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1u;
           if (!mbar_wait(full_bar(s), ph, abort_flag, (2u << 24) | (uint32_t)kb)) { ok = false; break; }
+          if (CONV && !mbar_wait(ready_bar(s), ph, abort_flag, (4u << 24) | (uint32_t)kb)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sj = ring + s * C::STAGE_BYTES, si = sj + C::J_BYTES;
           const uint64_t dj = kmajor_sw128_desc(sj), di = kmajor_sw128_desc(si);
 #pragma unroll
           for (int ks = 0; ks < STAGE_K_BYTES / MMA_K_BYTES; ++ks) {
             // stepping 32 bytes along K inside the swizzled row = +2 in the 16-byte address field
-            mma_ss<KIND>(d_tmem, dj + 2u * ks, di + 2u * ks, idesc, (kb | ks) != 0);
+            mma_ss<KIND>(d_tmem, dj + 2u * ks, di + 2u * ks, idesc_t, (kb | ks) != 0);
           }
           mma_commit(empty_bar(s));
         }
         if (ok) mma_commit(acc_full(buf));
+      }
+    }
+  } else if (CONV != 0 && warp >= 2 + EPI_WARPS) {
+    // ---------------- converter warps: raw FP8 rows -> BF16 rows in the swizzled K-major layout ----------------
+    // A raw row is 64 bytes = four 16-byte chunks; chunk c of row r (k = 16c .. 16c+15) becomes the two
+    // 16-byte chunks 2c, 2c+1 of the 128-byte BF16 row, which the 128-byte swizzle stores at chunk
+    // positions (2c) ^ (r & 7) and (2c+1) ^ (r & 7).
+    const int ct = threadIdx.x - 32 * (2 + EPI_WARPS);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < items && ok; t += gridDim.x) {
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int s = it % C::STAGES;
+        const uint32_t ph = (it / C::STAGES) & 1u;
+        ok = mbar_wait(full_bar(s), ph, abort_flag, (5u << 24) | (uint32_t)kb);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        uint8_t *stage = smem_raw + (ring - smem_u32(smem_raw)) + s * C::STAGE_BYTES;
+        const uint8_t *raw = stage + C::J_BYTES + C::I_BYTES;
+        uint8_t *dst = stage + (CONV == 1 ? C::J_BYTES : 0);
+#pragma unroll 2
+        for (int idx = ct; idx < C::RAW_ROWS * 4; idx += 32 * CONV_WARPS) {
+          const int r = idx >> 2, c = idx & 3;
+          const uint4 q = *reinterpret_cast<const uint4 *>(raw + idx * 16);
+          uint32_t w[8];
+          fp8x4_to_bf16x2<FT>(q.x, w[0], w[1]);
+          fp8x4_to_bf16x2<FT>(q.y, w[2], w[3]);
+          fp8x4_to_bf16x2<FT>(q.z, w[4], w[5]);
+          fp8x4_to_bf16x2<FT>(q.w, w[6], w[7]);
+          uint8_t *row = dst + r * 128;
+          *reinterpret_cast<uint4 *>(row + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4 *>(row + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready_bar(s));
       }
     }
   } else {
@@ -368,8 +442,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     float mx = 0.f;
     uint32_t lt = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++lt) {
-      const int i0 = (t % tiles_i) * BI, j0 = (t / tiles_i) * BM;
+    for (int t = blockIdx.x; t < items && ok; t += gridDim.x, ++lt) {
+      int i0, j0, rows;
+      item_at(t, i0, j0, rows);
       const uint32_t buf = lt & 1u, use = lt >> 1;
       ok = mbar_wait(acc_full(buf), use & 1u, abort_flag, (3u << 24) | (uint32_t)warp);
       ok = __all_sync(0xFFFFFFFFu, ok);
@@ -380,7 +455,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
       const float sbj = col_ok && o.sb_vec ? o.sb[j] : sb_const;
       const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BI;
       for (int c0 = half * (BI / 2); c0 < (half + 1) * (BI / 2); c0 += 32) {
-        if (i0 + c0 >= m) break;   // warp-uniform
+        if (c0 >= rows || i0 + c0 >= m) break;   // warp-uniform
         float acc[32];
         tmem_ld32(t_lane + c0, acc);
         if (col_ok) mx = fmaxf(mx, drain32<DT>(o, r, md, acc, i0 + c0, j, m, as_const, sbj));
@@ -428,87 +503,113 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// K-major operand: rows x k elements, row pitch ld elements; box = 128 bytes of K x box_rows rows
-static bool make_map(CUtensorMap *map, const void *base, int elem_bytes, int k, int rows, int ld, int box_rows) {
+// K-major operand: rows x k elements, row pitch ld elements.  Operands the MMA reads directly get
+// boxes of 128 bytes of K x box_rows rows with the 128-byte swizzle; an FP8 operand that is widened
+// in shared memory first (raw) gets plain 64-byte rows.
+static bool make_map(CUtensorMap *map, const void *base, int elem_bytes, int k, int rows, int ld, int box_rows, bool raw) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
-  const cuuint32_t box[2] = {(cuuint32_t)(STAGE_K_BYTES / elem_bytes), (cuuint32_t)box_rows};
+  const cuuint32_t box[2] = {(cuuint32_t)(raw ? STAGE_K_BYTES / 2 : STAGE_K_BYTES / elem_bytes), (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   return fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
-         CUDA_SUCCESS;
+            raw ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BI, int KIND, int DT>
-static cudaError_t launch_cfg(const CUtensorMap &mi, const CUtensorMap &mj, int m, int n, int k_bytes, uint32_t idesc,
-                              const OutDesc &o, const EpiMode &md, int sms, cudaStream_t s) {
-  using C = Cfg<BI>;
+template <int BI, int KIND, int DT, int CONV, int FT>
+static cudaError_t launch_cfg(const CUtensorMap &mi, const CUtensorMap &mj, const CUtensorMap &mih, int m, int n,
+                              int k_bytes, uint32_t idesc, uint32_t idesc_half, const OutDesc &o, const EpiMode &md, int sms,
+                              cudaStream_t s) {
+  using C = Cfg<BI, CONV>;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BI, KIND, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               C::SMEM_BYTES);
+    const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BI, KIND, DT, CONV, FT>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     attr_done[dev & 63] = true;
   }
   const int tiles = ((m + BI - 1) / BI) * ((n + BM - 1) / BM);
-  const int grid = tiles < sms ? tiles : sms;
-  gemm_tc_kernel<BI, KIND, DT><<<grid, THREADS, C::SMEM_BYTES, s>>>(mi, mj, m, n, k_bytes, idesc, o, md);
+  int grid = tiles < sms ? tiles : sms;
+  if (const char *g = getenv("E5MA_TC_GRID")) {   // experiments: fewer CTAs than SMs
+    const int v = atoi(g);
+    if (v > 0 && v < grid) grid = v;
+  }
+  gemm_tc_kernel<BI, KIND, DT, CONV, FT><<<grid, C::NTHREADS, C::SMEM_BYTES, s>>>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md);
   return cudaGetLastError();
 }
 
-template <int BI, int KIND>
-static cudaError_t launch_dt(const CUtensorMap &mi, const CUtensorMap &mj, int m, int n, int k_bytes, uint32_t idesc,
-                             const OutDesc &o, const EpiMode &md, int sms, cudaStream_t s) {
+template <int BI, int KIND, int CONV, int FT>
+static cudaError_t launch_dt(const CUtensorMap &mi, const CUtensorMap &mj, const CUtensorMap &mih, int m, int n,
+                             int k_bytes, uint32_t idesc, uint32_t idesc_half, const OutDesc &o, const EpiMode &md, int sms,
+                             cudaStream_t s) {
   switch (o.d_dtype) {
-    case E5MA_BF16: return launch_cfg<BI, KIND, E5MA_BF16>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
-    case E5MA_FP32: return launch_cfg<BI, KIND, E5MA_FP32>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
-    case E5MA_FP16: return launch_cfg<BI, KIND, E5MA_FP16>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
-    case E5MA_E5M2: return launch_cfg<BI, KIND, E5MA_E5M2>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
-    default: return launch_cfg<BI, KIND, E5MA_E4M3>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
+    case E5MA_BF16: return launch_cfg<BI, KIND, E5MA_BF16, CONV, FT>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
+    case E5MA_FP32: return launch_cfg<BI, KIND, E5MA_FP32, CONV, FT>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
+    case E5MA_FP16: return launch_cfg<BI, KIND, E5MA_FP16, CONV, FT>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
+    case E5MA_E5M2: return launch_cfg<BI, KIND, E5MA_E5M2, CONV, FT>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
+    default: return launch_cfg<BI, KIND, E5MA_E4M3, CONV, FT>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
   }
+}
+
+template <int BI>
+static cudaError_t launch_kind(int kind, int conv, int ft, const CUtensorMap &mi, const CUtensorMap &mj,
+                               const CUtensorMap &mih, int m, int n, int k_bytes, uint32_t idesc, uint32_t idesc_half,
+                               const OutDesc &o, const EpiMode &md, int sms, cudaStream_t s) {
+  if (kind == 0) return launch_dt<BI, 0, 0, E5MA_E5M2>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
+  if (conv == 0) return launch_dt<BI, 1, 0, E5MA_E5M2>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
+  if (conv == 1)
+    return ft == E5MA_E5M2 ? launch_dt<BI, 1, 1, E5MA_E5M2>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s)
+                           : launch_dt<BI, 1, 1, E5MA_E4M3>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
+  return ft == E5MA_E5M2 ? launch_dt<BI, 1, 2, E5MA_E5M2>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s)
+                         : launch_dt<BI, 1, 2, E5MA_E4M3>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
 }
 
 }  // namespace tc
 
 // Blackwell tile selection (takes the place of the reference's tuned per-architecture tables,
 // src/e5m2effma_tuned.h): tiles of 256 rows x 128 columns when they fill the machine or m is large,
-// else 128 x 128.
+// else 128 x 128.  Operand pairs: FP8 x FP8 -> kind::f8f6f4; BF16 x BF16 -> kind::f16; FP8 x BF16 in
+// either order -> kind::f16 with the FP8 side widened in shared memory.
 cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const uint8_t *A, int lda,
                            const uint8_t *B, int ldb, int m, int n, int k, const OutDesc &o, int sms,
                            cudaStream_t s) {
   using namespace tc;
   if (!a_kc || !b_kc || k <= 0) return cudaErrorNotSupported;
+  if (a_dtype == E5MA_FP32 || b_dtype == E5MA_FP32) return cudaErrorNotSupported;
   const bool f8 = is_fp8(a_dtype) && is_fp8(b_dtype);
-  const bool bf = a_dtype == E5MA_BF16 && b_dtype == E5MA_BF16;
-  if (!f8 && !bf) return cudaErrorNotSupported;
-  const int eb = f8 ? 1 : 2;
+  const int conv = f8 ? 0 : (is_fp8(a_dtype) ? 1 : (is_fp8(b_dtype) ? 2 : 0));
+  const int kind = f8 ? 0 : 1;
+  const int ft = conv == 1 ? a_dtype : (conv == 2 ? b_dtype : E5MA_E5M2);
   const int tiles256 = ((m + 255) / 256) * ((n + BM - 1) / BM);
   const bool wide = m > 128 && (tiles256 >= sms || m % 256 == 0 || m > 1024);
   const int bi = wide ? 256 : 128;
-  CUtensorMap mi, mj;
-  if (!make_map(&mi, A, eb, k, m, lda, bi) || !make_map(&mj, B, eb, k, n, ldb, BM)) return cudaErrorNotSupported;
+  CUtensorMap mi, mj, mih;   // mih: op(A) with half-height boxes, for the half tiles of the last round
+  if (!make_map(&mi, A, elem_bytes(a_dtype), k, m, lda, bi, conv == 1) ||
+      !make_map(&mj, B, elem_bytes(b_dtype), k, n, ldb, BM, conv == 2) ||
+      !make_map(&mih, A, elem_bytes(a_dtype), k, m, lda, bi / 2, conv == 1))
+    return cudaErrorNotSupported;
   // the MMA's A operand (M side) is op(B)^T, its B operand (N side) is op(A)
   const int fi = f8 ? (a_dtype == E5MA_E5M2 ? 1 : 0) : 1, fj = f8 ? (b_dtype == E5MA_E5M2 ? 1 : 0) : 1;
-  const uint32_t idesc = instr_desc(fj, fi, BM, bi);
-  const int k_bytes = k * eb;
+  const uint32_t idesc = instr_desc(fj, fi, BM, bi), idesc_half = instr_desc(fj, fi, BM, bi / 2);
+  const int k_bytes = k * (f8 ? 1 : 2);   // bytes of K per operand row as the MMA sees it
   // 16-byte vector access in the epilogue: D (and C, bias) bases and column pitches must allow it
   const auto vec_ok = [](const void *p, int ld, int dtype) {
     return ((uintptr_t)p & 15u) == 0 && ((size_t)ld * elem_bytes(dtype)) % 16 == 0;
   };
   EpiMode md;
+  md.split = wide ? 1 : 0;
+  if (const char *e = getenv("E5MA_TC_SPLIT")) md.split = atoi(e) && wide;   // experiments
   md.vec = vec_ok(o.d, o.ldd, o.d_dtype);
   if (o.c && !((o.c_dtype == E5MA_FP32 || o.c_dtype == E5MA_BF16) && vec_ok(o.c, o.ldc, o.c_dtype))) md.vec = 0;
   if (o.bias && !((o.bias_dtype == E5MA_FP32 || o.bias_dtype == E5MA_BF16) && ((uintptr_t)o.bias & 15u) == 0)) md.vec = 0;
   if (o.sa_vec && ((uintptr_t)o.sa & 15u)) md.vec = 0;
-  if (f8) return wide ? launch_dt<256, 0>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s)
-                      : launch_dt<128, 0>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
-  return wide ? launch_dt<256, 1>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s)
-              : launch_dt<128, 1>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
+  return wide ? launch_kind<256>(kind, conv, ft, mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s)
+              : launch_kind<128>(kind, conv, ft, mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
 }
 
 }  // namespace e5b

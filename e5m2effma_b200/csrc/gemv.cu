@@ -13,6 +13,7 @@
 //     contiguous bytes feed four consecutive MMAs without any shuffling;
 //   * the 8 per-warp partial tiles meet in shared memory in a fixed order (deterministic), then one
 //     thread per output runs the common epilogue and the block issues one amax atomic.
+#include <stdlib.h>
 #include "common.cuh"
 
 namespace e5b {
@@ -22,31 +23,6 @@ __device__ __forceinline__ uint4 ld_stream16(const void *p) {
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
   return r;
-}
-
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-
-// Four FP8 codes (bytes 0..3 of w, ascending k) -> BF16 pairs (k0,k1) and (k2,k3).
-// The 7 magnitude bits of a code, placed so that its exponent field lands in the BF16 exponent
-// field, are the BF16 encoding of value * 2^-112 (E5M2, bias 15 -> 127) or value * 2^-120 (E4M3,
-// bias 7 -> 127), subnormal codes included; one BF16 multiply by the power of two restores the value.
-template <int T>
-__device__ __forceinline__ void fp8x4_to_bf16x2(uint32_t w, uint32_t &lo, uint32_t &hi) {
-  const uint32_t p0 = __byte_perm(w, 0, 0x1404);   // (b1 << 24) | (b0 << 8)
-  const uint32_t p1 = __byte_perm(w, 0, 0x3424);   // (b3 << 24) | (b2 << 8)
-  if (T == E5MA_E5M2) {
-    const uint32_t k = 0x77807780u;                // 2^112 in both halves
-    lo = mul_bf16x2((p0 & 0x80008000u) | ((p0 >> 3) & 0x0FE00FE0u), k);
-    hi = mul_bf16x2((p1 & 0x80008000u) | ((p1 >> 3) & 0x0FE00FE0u), k);
-  } else {
-    const uint32_t k = 0x7B807B80u;                // 2^120 in both halves
-    lo = mul_bf16x2((p0 & 0x80008000u) | ((p0 >> 4) & 0x07F007F0u), k);
-    hi = mul_bf16x2((p1 & 0x80008000u) | ((p1 >> 4) & 0x07F007F0u), k);
-  }
 }
 
 __device__ __forceinline__ void mma_bf16_16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -60,7 +36,8 @@ __device__ __forceinline__ void mma_bf16_16816(float c[4], uint32_t a0, uint32_t
 constexpr int GV_WARPS = 8;
 
 // MT: 16-row tiles per block.  AT: dtype of W.  XT: dtype of X (E5M2, E4M3 or BF16).
-template <int MT, int AT, int XT>
+// U: k-steps whose loads are all issued before the first of them is consumed (bytes in flight).
+template <int MT, int AT, int XT, int U>
 __global__ void __launch_bounds__(GV_WARPS * 32) gemv_mma_kernel(const uint8_t *__restrict__ W, int lda,
                                                                  const uint8_t *__restrict__ X, int ldx, int m, int n,
                                                                  int k, OutDesc o) {
@@ -68,6 +45,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_mma_kernel(const uint8_t *
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * (MT * 16);
   constexpr int XB = XT == E5MA_BF16 ? 2 : 1;
+  constexpr int XW = XT == E5MA_BF16 ? 2 : 1;   // 16-byte loads of X per 16 elements
 
   float acc[MT][4];
 #pragma unroll
@@ -77,53 +55,61 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_mma_kernel(const uint8_t *
 
   const uint8_t *xcol = X + (size_t)g * ldx * XB;
   const bool xlive = g < n;
+  const uint8_t *wrow[MT][2];
+  bool wlive[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    const int ra = row0 + mt * 16 + g, rb = ra + 8;
+    wlive[mt][0] = ra < m; wlive[mt][1] = rb < m;
+    wrow[mt][0] = W + (size_t)(wlive[mt][0] ? ra : 0) * lda;
+    wrow[mt][1] = W + (size_t)(wlive[mt][1] ? rb : 0) * lda;
+  }
 
   // A warp's step covers bytes [kc, kc + 128) of every row; this lane owns 16 bytes in each half.
   // The trip count must be the same for all lanes of the warp (mma.sync is warp-collective), so the
   // loop runs on the warp-uniform kc and the per-lane offset only enters the load predicates.
-#pragma unroll 2
-  for (int kc = warp * 128; kc < k; kc += GV_WARPS * 128) {
-    const int kb = kc + t * 16;
-    uint4 wa[MT][2], wb[MT][2];
-    uint32_t xw[2][8];
+  for (int kc0 = warp * 128; kc0 < k; kc0 += U * GV_WARPS * 128) {
+    uint4 wq[U][2][MT][2];      // [step][half][tile][row g / g+8]
+    uint4 xq[U][2][XW];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int kk = kb + h * 64;
-      const bool kin = kk < k;
+    for (int u = 0; u < U; ++u)
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        const int ra = row0 + mt * 16 + g, rb = ra + 8;
-        wa[mt][h] = kin && ra < m ? ld_stream16(W + (size_t)ra * lda + kk) : make_uint4(0, 0, 0, 0);
-        wb[mt][h] = kin && rb < m ? ld_stream16(W + (size_t)rb * lda + kk) : make_uint4(0, 0, 0, 0);
+      for (int h = 0; h < 2; ++h) {
+        const int kk = kc0 + u * GV_WARPS * 128 + t * 16 + h * 64;
+        const bool kin = kk < k;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int r = 0; r < 2; ++r)
+            wq[u][h][mt][r] = kin && wlive[mt][r] ? ld_stream16(wrow[mt][r] + kk) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int q = 0; q < XW; ++q)
+          xq[u][h][q] = kin && xlive ? __ldg(reinterpret_cast<const uint4 *>(xcol + (size_t)kk * XB) + q) : make_uint4(0, 0, 0, 0);
       }
-      if (XT == E5MA_BF16) {
-        uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
-        if (kin && xlive) {
-          const uint4 *xp = reinterpret_cast<const uint4 *>(xcol + (size_t)kk * 2);
-          x0 = __ldg(xp); x1 = __ldg(xp + 1);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t xw[8];
+        if (XT == E5MA_BF16) {
+          xw[0] = xq[u][h][0].x; xw[1] = xq[u][h][0].y; xw[2] = xq[u][h][0].z; xw[3] = xq[u][h][0].w;
+          xw[4] = xq[u][h][XW - 1].x; xw[5] = xq[u][h][XW - 1].y; xw[6] = xq[u][h][XW - 1].z; xw[7] = xq[u][h][XW - 1].w;
+        } else {
+          const uint32_t q[4] = {xq[u][h][0].x, xq[u][h][0].y, xq[u][h][0].z, xq[u][h][0].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) fp8x4_to_bf16x2<XT == E5MA_BF16 ? E5MA_E5M2 : XT>(q[e], xw[2 * e], xw[2 * e + 1]);
         }
-        xw[h][0] = x0.x; xw[h][1] = x0.y; xw[h][2] = x0.z; xw[h][3] = x0.w;
-        xw[h][4] = x1.x; xw[h][5] = x1.y; xw[h][6] = x1.z; xw[h][7] = x1.w;
-      } else {
-        uint4 x0 = make_uint4(0, 0, 0, 0);
-        if (kin && xlive) x0 = __ldg(reinterpret_cast<const uint4 *>(xcol + kk));
-        const uint32_t q[4] = {x0.x, x0.y, x0.z, x0.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) fp8x4_to_bf16x2<XT == E5MA_BF16 ? E5MA_E5M2 : XT>(q[e], xw[h][2 * e], xw[h][2 * e + 1]);
-      }
-    }
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint32_t qa[4] = {wq[u][h][mt][0].x, wq[u][h][mt][0].y, wq[u][h][mt][0].z, wq[u][h][mt][0].w};
+          const uint32_t qb[4] = {wq[u][h][mt][1].x, wq[u][h][mt][1].y, wq[u][h][mt][1].z, wq[u][h][mt][1].w};
 #pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        const uint32_t qa[4] = {wa[mt][h].x, wa[mt][h].y, wa[mt][h].z, wa[mt][h].w};
-        const uint32_t qb[4] = {wb[mt][h].x, wb[mt][h].y, wb[mt][h].z, wb[mt][h].w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          uint32_t a0, a2, a1, a3;
-          fp8x4_to_bf16x2<AT>(qa[e], a0, a2);   // row g:   k pairs (0,1) and (2,3) of this word
-          fp8x4_to_bf16x2<AT>(qb[e], a1, a3);   // row g+8
-          mma_bf16_16816(acc[mt], a0, a1, a2, a3, xw[h][2 * e], xw[h][2 * e + 1]);
+          for (int e = 0; e < 4; ++e) {
+            uint32_t a0, a2, a1, a3;
+            fp8x4_to_bf16x2<AT>(qa[e], a0, a2);   // row g:   k pairs (0,1) and (2,3) of this word
+            fp8x4_to_bf16x2<AT>(qb[e], a1, a3);   // row g+8
+            mma_bf16_16816(acc[mt], a0, a1, a2, a3, xw[2 * e], xw[2 * e + 1]);
+          }
         }
       }
   }
@@ -152,24 +138,36 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_mma_kernel(const uint8_t *
   if (o.amax) block_amax(o.amax, mx);
 }
 
-template <int MT, int AT>
-static cudaError_t gemv_x(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
-                          const OutDesc &o, cudaStream_t s) {
+template <int MT, int AT, int U>
+static cudaError_t gemv_xu(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
+                           const OutDesc &o, cudaStream_t s) {
   const unsigned grid = (unsigned)((m + MT * 16 - 1) / (MT * 16));
   switch (x_dtype) {
-    case E5MA_BF16: gemv_mma_kernel<MT, AT, E5MA_BF16><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, X, ldx, m, n, k, o); break;
-    case E5MA_E5M2: gemv_mma_kernel<MT, AT, E5MA_E5M2><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, X, ldx, m, n, k, o); break;
-    case E5MA_E4M3: gemv_mma_kernel<MT, AT, E5MA_E4M3><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, X, ldx, m, n, k, o); break;
+    case E5MA_BF16: gemv_mma_kernel<MT, AT, E5MA_BF16, U><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, X, ldx, m, n, k, o); break;
+    case E5MA_E5M2: gemv_mma_kernel<MT, AT, E5MA_E5M2, U><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, X, ldx, m, n, k, o); break;
+    case E5MA_E4M3: gemv_mma_kernel<MT, AT, E5MA_E4M3, U><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, X, ldx, m, n, k, o); break;
     default: return cudaErrorNotSupported;
   }
   return cudaGetLastError();
+}
+
+// U = 2 k-steps in flight per warp when K is long enough to have them; E5MA_GEMV_U (experiments) overrides
+template <int MT, int AT>
+static cudaError_t gemv_x(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
+                          const OutDesc &o, cudaStream_t s) {
+  int u = k >= 4096 ? 2 : 1;
+  if (const char *e = getenv("E5MA_GEMV_U")) u = atoi(e);
+  if (u >= 4 && MT == 1) return gemv_xu<MT, AT, MT == 1 ? 4 : 2>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
+  if (u >= 2) return gemv_xu<MT, AT, 2>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
+  return gemv_xu<MT, AT, 1>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
 }
 
 // Rows per block: 16 keeps more blocks in flight (m / 16 of them); 32 halves how often X is
 // re-read from L2, which matters once X is no longer tiny next to a block's share of W.
 cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx,
                             int m, int n, int k, const OutDesc &o, int sms, cudaStream_t s) {
-  const bool wide = n > 2 && m >= sms * 32;
+  bool wide = n > 2 && m >= sms * 32;
+  if (const char *e = getenv("E5MA_GEMV_MT")) wide = atoi(e) == 2;   // experiments
   if (a_dtype == E5MA_E5M2)
     return wide ? gemv_x<2, E5MA_E5M2>(x_dtype, A, lda, X, ldx, m, n, k, o, s)
                 : gemv_x<1, E5MA_E5M2>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
