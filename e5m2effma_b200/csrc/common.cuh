@@ -45,30 +45,36 @@ __device__ __forceinline__ void dec_fp8x4(uint32_t w, float v[4]) {
   v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
 
-// ---- FP8 -> BF16 widening (tensor-core operands) ------------------------------------------------
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
+// ---- FP8 -> FP32 / BF16 widening of packed codes -----------------------------------------------
+// Four FP8 codes (bytes 0..3 of w, ascending k) -> four FP32 values, exact, subnormal codes included.
+// E5M2 is the upper byte of an FP16, so masking puts codes 1, 3 (and, shifted, 0, 2) in place as FP16
+// pairs; E4M3 pairs go through the hardware FP8 -> FP16 converter.  Then FP16 -> FP32 conversions.
+// Most of the work runs on the floating-point pipes; the integer pipe only sees two operations.
+template <int T>
+__device__ __forceinline__ void fp8x4_to_f32(uint32_t w, float f[4]) {
+  uint32_t h02, h13;   // FP16 pairs (code 0 | code 2) and (code 1 | code 3), or (0 | 1) and (2 | 3) for E4M3
+  if (T == E5MA_E5M2) {
+    h13 = w & 0xFF00FF00u;
+    h02 = __byte_perm(w, 0, 0x2404);   // (b2 << 24) | (b0 << 8)
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&h02));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&h13));
+    f[0] = a.x; f[2] = a.y; f[1] = b.x; f[3] = b.y;
+  } else {
+    h02 = e4m3x2_to_f16x2(w);          // codes 0, 1
+    h13 = e4m3x2_to_f16x2(w >> 16);    // codes 2, 3
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&h02));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&h13));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  }
 }
-
-// Four FP8 codes (bytes 0..3 of w, ascending k) -> BF16 pairs (k0,k1) and (k2,k3).
-// The 7 magnitude bits of a code, placed so that its exponent field lands in the BF16 exponent
-// field, are the BF16 encoding of value * 2^-112 (E5M2, bias 15 -> 127) or value * 2^-120 (E4M3,
-// bias 7 -> 127), subnormal codes included; one BF16 multiply by the power of two restores the value.
+// ... -> BF16 pairs (k0,k1) and (k2,k3): an FP8 value has at most 4 significant bits, so the upper
+// half of its FP32 encoding is its exact BF16 encoding; one byte permute packs two of them.
 template <int T>
 __device__ __forceinline__ void fp8x4_to_bf16x2(uint32_t w, uint32_t &lo, uint32_t &hi) {
-  const uint32_t p0 = __byte_perm(w, 0, 0x1404);   // (b1 << 24) | (b0 << 8)
-  const uint32_t p1 = __byte_perm(w, 0, 0x3424);   // (b3 << 24) | (b2 << 8)
-  if (T == E5MA_E5M2) {
-    const uint32_t k = 0x77807780u;                // 2^112 in both halves
-    lo = mul_bf16x2((p0 & 0x80008000u) | ((p0 >> 3) & 0x0FE00FE0u), k);
-    hi = mul_bf16x2((p1 & 0x80008000u) | ((p1 >> 3) & 0x0FE00FE0u), k);
-  } else {
-    const uint32_t k = 0x7B807B80u;                // 2^120 in both halves
-    lo = mul_bf16x2((p0 & 0x80008000u) | ((p0 >> 4) & 0x07F007F0u), k);
-    hi = mul_bf16x2((p1 & 0x80008000u) | ((p1 >> 4) & 0x07F007F0u), k);
-  }
+  float f[4];
+  fp8x4_to_f32<T>(w, f);
+  lo = __byte_perm(__float_as_uint(f[0]), __float_as_uint(f[1]), 0x7632);
+  hi = __byte_perm(__float_as_uint(f[2]), __float_as_uint(f[3]), 0x7632);
 }
 
 // ---- encode --------------------------------------------------------------------------------
