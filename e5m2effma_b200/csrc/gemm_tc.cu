@@ -95,8 +95,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     int tile = item, hf = 0;
     rows = BI;
     if (split && item >= full_items) { const int h = item - full_items; tile = full_items + (h >> 1); hf = h & 1; rows = BI / 2; }
-    i0 = (tile % tiles_i) * BI + hf * (BI / 2);
-    j0 = (tile / tiles_i) * BM;
+    int ti, tj;
+    tile_coords(tile, tiles_i, tiles_j, ti, tj);
+    i0 = ti * BI + hf * (BI / 2);
+    j0 = tj * BM;
   };
 
   if (threadIdx.x == 0) {
@@ -324,26 +326,30 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   const int kind = f8 ? 0 : 1;
   const int ft = conv == 1 ? a_dtype : (conv == 2 ? b_dtype : E5MA_E5M2);
   // CTA pairs (gemm_tc2.cuh) for big unmixed problems: 256 x 256 tiles, half the operand bytes per CTA
-  int use_pair = 0;
-  if (const char *e = getenv("E5MA_TC_PAIR")) use_pair = atoi(e);
-  if (use_pair && conv == 0 && m >= 512 && n >= 512 && ((m + 255) / 256) * ((n + 255) / 256) >= sms / 4) {
-    CUtensorMap pi, pj;
+  int use_pair = 1;
+  if (const char *e = getenv("E5MA_TC_PAIR")) use_pair = atoi(e);   // experiments: 0 keeps every problem on single CTAs
+  if (use_pair && conv == 0 && m >= 512 && n >= 512 && ((m + 255) / 256) * ((n + 255) / 256) >= sms / 2) {
+    CUtensorMap pi, pj, pi2, pi4;
     if (!make_map(&pi, A, elem_bytes(a_dtype), k, m, lda, 128, false) ||
-        !make_map(&pj, B, elem_bytes(b_dtype), k, n, ldb, 128, false))
+        !make_map(&pj, B, elem_bytes(b_dtype), k, n, ldb, 128, false) ||
+        !make_map(&pi2, A, elem_bytes(a_dtype), k, m, lda, 64, false) ||
+        !make_map(&pi4, A, elem_bytes(a_dtype), k, m, lda, 32, false))
       return cudaErrorNotSupported;
     const int fi2 = f8 ? (a_dtype == E5MA_E5M2 ? 1 : 0) : 1, fj2 = f8 ? (b_dtype == E5MA_E5M2 ? 1 : 0) : 1;
     const auto vec_ok2 = [](const void *p, int ld, int dtype) {
       return ((uintptr_t)p & 15u) == 0 && ((size_t)ld * elem_bytes(dtype)) % 16 == 0;
     };
     EpiMode pm;
-    pm.split = 0;
+    pm.split = 1;
+    if (const char *e = getenv("E5MA_TC_SPLIT")) pm.split = atoi(e);
     pm.vec = vec_ok2(o.d, o.ldd, o.d_dtype);
     if (o.c && !((o.c_dtype == E5MA_FP32 || o.c_dtype == E5MA_BF16) && vec_ok2(o.c, o.ldc, o.c_dtype))) pm.vec = 0;
     if (o.bias && !((o.bias_dtype == E5MA_FP32 || o.bias_dtype == E5MA_BF16) && ((uintptr_t)o.bias & 15u) == 0)) pm.vec = 0;
     if (o.sa_vec && ((uintptr_t)o.sa & 15u)) pm.vec = 0;
     const uint32_t pdesc = instr_desc(fj2, fi2, 256, 256);
-    return f8 ? launch_pair<0>(pi, pj, m, n, k * 1, pdesc, o, pm, sms, s)
-              : launch_pair<1>(pi, pj, m, n, k * 2, pdesc, o, pm, sms, s);
+    const PairSplit ps = {instr_desc(fj2, fi2, 256, 128), instr_desc(fj2, fi2, 256, 64)};
+    return f8 ? launch_pair<0>(pi, pj, pi2, pi4, m, n, k * 1, pdesc, ps, o, pm, sms, s)
+              : launch_pair<1>(pi, pj, pi2, pi4, m, n, k * 2, pdesc, ps, o, pm, sms, s);
   }
   const int tiles256 = ((m + 255) / 256) * ((n + BM - 1) / BM);
   const bool wide = m > 128 && (tiles256 >= sms || m % 256 == 0 || m > 1024);

@@ -79,11 +79,17 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols)
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 
-// map_i / map_j: tensor maps of op(A) / op(B)^T with boxes of 128 rows x 128 bytes of K.
+// What the kernel needs to cut the tiles of the last, partly filled round into 2 or 4 slices along
+// i: MMA N = 256 / f, boxes of 128 / f rows of op(A) per CTA.
+struct PairSplit { uint32_t idesc2, idesc4; };
+
+// map_i / map_j: tensor maps of op(A) / op(B)^T with boxes of 128 rows x 128 bytes of K;
+// map_i2 / map_i4: op(A) with boxes of 64 / 32 rows (sliced tiles of the last round).
 template <int KIND, int DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant__ CUtensorMap map_j, int m, int n,
-                    int k_bytes, uint32_t idesc, OutDesc o, EpiMode md) {
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant__ CUtensorMap map_j,
+                    const __grid_constant__ CUtensorMap map_i2, const __grid_constant__ CUtensorMap map_i4, int m, int n,
+                    int k_bytes, uint32_t idesc, PairSplit ps, OutDesc o, EpiMode md) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *after_ring = smem_raw + (ring - smem_u32(smem_raw)) + P_STAGES * P_STAGE_BYTES;
@@ -101,6 +107,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
   const int tiles_i = (m + P_TILE - 1) / P_TILE, tiles_j = (n + P_TILE - 1) / P_TILE, tiles = tiles_i * tiles_j;
   const int kblocks = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
+
+  // Work items: tiles dealt round-robin to the pairs.  When the last round would leave most pairs idle,
+  // its tiles are cut into f = 2 or 4 slices of 256 / f rows i (the largest f with f * rest <= pairs), so
+  // that the round takes 1 / f of the time.  Every role of both CTAs derives the same list.
+  const int full_items = (tiles / pairs) * pairs, rest = tiles - full_items;
+  const int f = (md.split && rest > 0) ? (4 * rest <= pairs ? 4 : (2 * rest <= pairs ? 2 : 1)) : 1;
+  const int items = full_items + f * rest;
+  const auto item_at = [&](int item, int &i0, int &j0, int &cols) {
+    int tile = item, sub = 0;
+    cols = P_TILE;
+    if (item >= full_items) { const int h = item - full_items; tile = full_items + h / f; sub = h % f; cols = P_TILE / f; }
+    int ti, tj;
+    tile_coords(tile, tiles_i, tiles_j, ti, tj);
+    i0 = ti * P_TILE + sub * cols;
+    j0 = tj * P_TILE;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -124,18 +146,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = pair; t < tiles && ok; t += pairs) {
-        const int i0 = (t % tiles_i) * P_TILE + (int)rank * 128, j0 = (t / tiles_i) * P_TILE + (int)rank * 128;
+      for (int t = pair; t < items && ok; t += pairs) {
+        int i0, j0, cols;
+        item_at(t, i0, j0, cols);
+        i0 += (int)rank * (cols / 2);     // this CTA's half of the N side
+        j0 += (int)rank * 128;            // and its 128 rows of the M side
+        const CUtensorMap *mi = cols == P_TILE ? &map_i : (cols == P_TILE / 2 ? &map_i2 : &map_i4);
+        const uint32_t pair_bytes = 2u * (P_HALF_BYTES + (uint32_t)(cols / 2) * STAGE_K_BYTES);
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)kb)) { ok = false; break; }
           const uint32_t lead_full = map_to_rank(full_bar(s), 0);
-          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * P_STAGE_BYTES);   // both CTAs' bytes land on this barrier
+          if (rank == 0) mbar_expect_tx(full_bar(s), pair_bytes);   // both CTAs' bytes land on this barrier
           const uint32_t sj = ring + s * P_STAGE_BYTES, si = sj + P_HALF_BYTES;
           const int kc = kb * (KIND == 0 ? STAGE_K_BYTES : STAGE_K_BYTES / 2);
           tma_load_2d_pair(sj, &map_j, kc, j0, lead_full);
-          tma_load_2d_pair(si, &map_i, kc, i0, lead_full);
+          tma_load_2d_pair(si, mi, kc, i0, lead_full);
         }
       }
     }
@@ -144,7 +171,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
     if (lane == 0 && rank == 0) {
       uint32_t it = 0, lt = 0;
       bool ok = true;
-      for (int t = pair; t < tiles && ok; t += pairs, ++lt) {
+      for (int t = pair; t < items && ok; t += pairs, ++lt) {
+        int i0, j0, cols;
+        item_at(t, i0, j0, cols);
+        const uint32_t idesc_t = cols == P_TILE ? idesc : (cols == P_TILE / 2 ? ps.idesc2 : ps.idesc4);
         const uint32_t buf = lt & 1u, use = lt >> 1;
         if (!mbar_wait(acc_empty(buf), (use & 1u) ^ 1u, abort_flag, (2u << 24) | 0xFFFFu)) { ok = false; break; }
         tc_fence_after();
@@ -158,7 +188,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
           const uint64_t dj = kmajor_sw128_desc(sj), di = kmajor_sw128_desc(si);
 #pragma unroll
           for (int ks = 0; ks < STAGE_K_BYTES / MMA_K_BYTES; ++ks)
-            mma_ss_pair<KIND>(d_tmem, dj + 2u * ks, di + 2u * ks, idesc, (kb | ks) != 0);
+            mma_ss_pair<KIND>(d_tmem, dj + 2u * ks, di + 2u * ks, idesc_t, (kb | ks) != 0);
           mma_commit_pair(empty_bar(s));                   // this CTA's stage is free again
           mma_commit_pair(map_to_rank(empty_bar(s), 1));   // and the peer's
         }
@@ -177,8 +207,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
     float mx = 0.f;
     uint32_t lt = 0;
     bool ok = true;
-    for (int t = pair; t < tiles && ok; t += pairs, ++lt) {
-      const int i0 = (t % tiles_i) * P_TILE, j0 = (t / tiles_i) * P_TILE + (int)rank * 128;
+    for (int t = pair; t < items && ok; t += pairs, ++lt) {
+      int i0, j0, cols;
+      item_at(t, i0, j0, cols);
+      j0 += (int)rank * 128;
       const uint32_t buf = lt & 1u, use = lt >> 1;
       ok = mbar_wait(acc_full(buf), use & 1u, abort_flag, (3u << 24) | (uint32_t)warp);
       ok = __all_sync(0xFFFFFFFFu, ok);
@@ -189,7 +221,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
       const float sbj = col_ok && o.sb_vec ? o.sb[j] : sb_const;
       const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * P_TILE;
       for (int c0 = half * (P_TILE / 2); c0 < (half + 1) * (P_TILE / 2); c0 += 32) {
-        if (i0 + c0 >= m) break;   // warp-uniform
+        if (c0 >= cols || i0 + c0 >= m) break;   // warp-uniform
         float acc[32];
         tmem_ld32(t_lane + c0, acc);
         if (col_ok) mx = fmaxf(mx, drain32<DT>(o, r, md, acc, i0 + c0, j, m, as_const, sbj));
@@ -221,8 +253,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
 }
 
 template <int KIND, int DT>
-static cudaError_t launch_pair_cfg(const CUtensorMap &mi, const CUtensorMap &mj, int m, int n, int k_bytes, uint32_t idesc,
-                                   const OutDesc &o, const EpiMode &md, int sms, cudaStream_t s) {
+static cudaError_t launch_pair_cfg(const CUtensorMap &mi, const CUtensorMap &mj, const CUtensorMap &mi2, const CUtensorMap &mi4,
+                                   int m, int n, int k_bytes, uint32_t idesc, const PairSplit &ps, const OutDesc &o,
+                                   const EpiMode &md, int sms, cudaStream_t s) {
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -235,19 +268,20 @@ static cudaError_t launch_pair_cfg(const CUtensorMap &mi, const CUtensorMap &mj,
   const int tiles = ((m + P_TILE - 1) / P_TILE) * ((n + P_TILE - 1) / P_TILE);
   int pairs = sms / 2;
   if (tiles < pairs) pairs = tiles;
-  gemm_tc_pair_kernel<KIND, DT><<<2 * pairs, THREADS, P_SMEM_BYTES, s>>>(mi, mj, m, n, k_bytes, idesc, o, md);
+  gemm_tc_pair_kernel<KIND, DT><<<2 * pairs, THREADS, P_SMEM_BYTES, s>>>(mi, mj, mi2, mi4, m, n, k_bytes, idesc, ps, o, md);
   return cudaGetLastError();
 }
 
 template <int KIND>
-static cudaError_t launch_pair(const CUtensorMap &mi, const CUtensorMap &mj, int m, int n, int k_bytes, uint32_t idesc,
-                               const OutDesc &o, const EpiMode &md, int sms, cudaStream_t s) {
+static cudaError_t launch_pair(const CUtensorMap &mi, const CUtensorMap &mj, const CUtensorMap &mi2, const CUtensorMap &mi4,
+                               int m, int n, int k_bytes, uint32_t idesc, const PairSplit &ps, const OutDesc &o,
+                               const EpiMode &md, int sms, cudaStream_t s) {
   switch (o.d_dtype) {
-    case E5MA_BF16: return launch_pair_cfg<KIND, E5MA_BF16>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
-    case E5MA_FP32: return launch_pair_cfg<KIND, E5MA_FP32>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
-    case E5MA_FP16: return launch_pair_cfg<KIND, E5MA_FP16>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
-    case E5MA_E5M2: return launch_pair_cfg<KIND, E5MA_E5M2>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
-    default: return launch_pair_cfg<KIND, E5MA_E4M3>(mi, mj, m, n, k_bytes, idesc, o, md, sms, s);
+    case E5MA_BF16: return launch_pair_cfg<KIND, E5MA_BF16>(mi, mj, mi2, mi4, m, n, k_bytes, idesc, ps, o, md, sms, s);
+    case E5MA_FP32: return launch_pair_cfg<KIND, E5MA_FP32>(mi, mj, mi2, mi4, m, n, k_bytes, idesc, ps, o, md, sms, s);
+    case E5MA_FP16: return launch_pair_cfg<KIND, E5MA_FP16>(mi, mj, mi2, mi4, m, n, k_bytes, idesc, ps, o, md, sms, s);
+    case E5MA_E5M2: return launch_pair_cfg<KIND, E5MA_E5M2>(mi, mj, mi2, mi4, m, n, k_bytes, idesc, ps, o, md, sms, s);
+    default: return launch_pair_cfg<KIND, E5MA_E4M3>(mi, mj, mi2, mi4, m, n, k_bytes, idesc, ps, o, md, sms, s);
   }
 }
 

@@ -155,7 +155,7 @@ static cudaError_t gemv_xu(int x_dtype, const uint8_t *A, int lda, const uint8_t
 template <int MT, int AT>
 static cudaError_t gemv_x(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
                           const OutDesc &o, cudaStream_t s) {
-  int u = k >= 4096 ? 2 : 1;
+  int u = 1;   // measured on B200: one k-step per warp in flight (more registers cost occupancy and lose)
   if (const char *e = getenv("E5MA_GEMV_U")) u = atoi(e);
   if (u >= 4 && MT == 1) return gemv_xu<MT, AT, MT == 1 ? 4 : 2>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
   if (u >= 2) return gemv_xu<MT, AT, 2>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
@@ -166,7 +166,8 @@ static cudaError_t gemv_x(int x_dtype, const uint8_t *A, int lda, const uint8_t 
 // re-read from L2, which matters once X is no longer tiny next to a block's share of W.
 cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx,
                             int m, int n, int k, const OutDesc &o, int sms, cudaStream_t s) {
-  bool wide = n > 2 && m >= sms * 32;
+  bool wide = false;   // measured on B200: 16 rows per block wins for every n <= 8 (more blocks, fewer registers)
+  (void)sms;
   if (const char *e = getenv("E5MA_GEMV_MT")) wide = atoi(e) == 2;   // experiments
   if (a_dtype == E5MA_E5M2)
     return wide ? gemv_x<2, E5MA_E5M2>(x_dtype, A, lda, X, ldx, m, n, k, o, s)

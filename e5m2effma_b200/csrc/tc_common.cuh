@@ -101,6 +101,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float v[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Tile order.  Tiles are numbered so that GROUP_I consecutive tile rows (along i) are swept across all
+// tile columns before the next group starts: the CTAs that run at the same time then share a band of
+// op(A) that stays in L2 while op(B) streams past it, instead of re-reading all of op(A) from HBM for
+// every few tile columns (which a plain i-fastest order does once op(A) outgrows the 126 MB L2).
+constexpr int GROUP_I = 8;
+__device__ __forceinline__ void tile_coords(int t, int tiles_i, int tiles_j, int &ti, int &tj) {
+  const int per_group = GROUP_I * tiles_j;
+  const int g = t / per_group, r = t - g * per_group;
+  const int gi0 = g * GROUP_I;
+  const int gsize = tiles_i - gi0 < GROUP_I ? tiles_i - gi0 : GROUP_I;
+  ti = gi0 + r % gsize;
+  tj = r / gsize;
+}
+
 // Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the 128-byte
 // swizzle (what a TMA box of 128 bytes x R rows produces): 8-row groups are 1024 bytes apart (SBO),
 // the leading offset is not used by swizzled K-major layouts (encoded as 1), descriptor version 1,
