@@ -292,8 +292,6 @@ def main():
             step(i)
     e1.record(stream)
     barrier()
-    sampler.stop_flag = True
-    sampler.join()
     ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([ms], device=dev)
@@ -314,22 +312,61 @@ def main():
         h2d = sum(t.numel() * t.element_size() for t in ins)
         d2h = sum(t.numel() * t.element_size() for t in outs)
 
-        def e2e_step(i):
-            for d, h in zip(ins, host_in):
-                d.copy_(h, non_blocking=True)
-            w.launch(sptr)
-            if world > 1 and amax_t is not None:
-                dist.all_reduce(amax_t, op=dist.ReduceOp.MAX)
-            for h, d in zip(host_out, outs):
-                h.copy_(d, non_blocking=True)
+        # Two sets of device buffers and three streams: the upload of step i+1 and the read-back of step i-1
+        # overlap the kernel of step i.  Every step still moves all of its inputs and its result.
+        sets = []
+        for b in range(2):
+            if w.kind == "gemm":
+                dA, dB, dD = (w.A, w.B, w.D) if b == 0 else (w.A.clone(), w.B.clone(), w.D.clone())
+                swap = {id(w.A): dA, id(w.B): dB, id(w.D): dD}
+                sets.append({"ins": [swap.get(id(t), t) for t in ins], "outs": [swap.get(id(t), t) for t in outs],
+                             "launch": (lambda st, a=dA, bb=dB, d=dD: w.launch(st, a, bb, d))})
+            else:
+                sets.append({"ins": ins, "outs": outs, "launch": (lambda st: w.launch(st))})
+        s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_run = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
+        for e in ev_run + ev_out:
+            e.record(stream)
 
-        ksteps = max(3, min(args.steps, 10))
+        def e2e_step(i):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_run[b])          # the kernel that last read this buffer set is done
+                for d, h in zip(sets[b]["ins"], host_in):
+                    d.copy_(h, non_blocking=True)
+                ev_in[b].record(s_in)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ev_in[b])
+                s_run.wait_event(ev_out[b])         # the previous result of this set has been read back
+                sets[b]["launch"](s_run.cuda_stream)
+                if world > 1 and amax_t is not None:
+                    dist.all_reduce(amax_t, op=dist.ReduceOp.MAX)
+                ev_run[b].record(s_run)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_run[b])
+                for h, d in zip(host_out, sets[b]["outs"]):
+                    h.copy_(d, non_blocking=True)
+                ev_out[b].record(s_out)
+
+        def e2e_join():
+            for st in (s_in, s_run, s_out):
+                stream.wait_stream(st)
+
+        ksteps = max(4, min(args.steps, 10))
+        for st in (s_in, s_run, s_out):
+            st.wait_stream(stream)
         for i in range(2):
             e2e_step(i)
+        e2e_join()
         barrier()
         e0.record(stream)
+        for st in (s_in, s_run, s_out):
+            st.wait_stream(stream)
         for i in range(ksteps):
             e2e_step(i)
+        e2e_join()
         e1.record(stream)
         barrier()
         ems = e0.elapsed_time(e1)
@@ -338,11 +375,24 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ems = float(t.item())
         e2e = {"value": w.units * world / (ems / ksteps * 1e-3) / scale_div, "unit": unit, "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": ems / ksteps, "steps": ksteps}
+               "d2h_bytes_per_step": d2h, "ms_per_step": ems / ksteps, "steps": ksteps,
+               "pipeline": "2 buffer sets, upload / kernel / read-back on separate streams"}
+
+    sampler.stop_flag = True     # clocks were sampled through both timed regions (device-resident and end-to-end)
+    sampler.join()
+
+    def finish():
+        """Leave without tearing NCCL down: destroying the process group while an instantiated CUDA graph
+        still holds captured collectives has hung at exit; every rank meets once more and exits."""
+        sys.stdout.flush()
+        sys.stderr.flush()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+            os._exit(0)
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        finish()
         return
 
     pk = peaks()
@@ -377,8 +427,7 @@ def main():
                          "output of the small cases and on sampled rows/columns at full size); casts, AdamW: bit-exact",
             "gemm_fault": fault}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    finish()
 
 
 if __name__ == "__main__":
