@@ -138,6 +138,145 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_mma_kernel(const uint8_t *
   if (o.amax) block_amax(o.amax, mx);
 }
 
+// ---- the same computation with an asynchronous weight pipeline ---------------------------------
+// Every lane copies its own fragments (rows g and g+8, two 16-byte pieces of a warp's 128-byte k-step)
+// with cp.async straight into a private shared-memory slot, GA_STAGES k-steps ahead, and reads them
+// back when their group has landed.  The bytes in flight no longer occupy registers (the kernel
+// above needs 64-80 registers for its load buffers, which caps it at 3-4 blocks per SM and leaves
+// every warp waiting on its own loads); no barrier is involved because a lane only ever reads
+// what it copied itself.  Out-of-range rows and k positions are copied with a source size of 0,
+// which zero-fills the slot.
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, bool live) {
+  const int bytes = live ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int AT, int XT, int GA_STAGES>
+__global__ void __launch_bounds__(GV_WARPS * 32) gemv_async_kernel(const uint8_t *__restrict__ W, int lda,
+                                                                   const uint8_t *__restrict__ X, int ldx, int m, int n,
+                                                                   int k, OutDesc o) {
+  extern __shared__ __align__(16) uint8_t ring_raw[];        // [warp][stage][fragment 0..3][lane] x 16 bytes
+  __shared__ float red[GV_WARPS][16][9];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * 16;
+  constexpr int XB = XT == E5MA_BF16 ? 2 : 1;
+  constexpr int XW = XT == E5MA_BF16 ? 2 : 1;
+  uint8_t *my_ring = ring_raw + (size_t)warp * GA_STAGES * 2048 + lane * 16;
+  const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
+
+  const int ra = row0 + g, rb = ra + 8;
+  const bool la = ra < m, lb = rb < m;
+  const uint8_t *wa = W + (size_t)(la ? ra : 0) * lda, *wb = W + (size_t)(lb ? rb : 0) * lda;
+  // this warp's k-steps: 128 bytes at kc = (warp + 8 * it) * 128
+  const int steps = k > warp * 128 ? (k - warp * 128 + GV_WARPS * 128 - 1) / (GV_WARPS * 128) : 0;
+  const auto issue = [&](int it) {
+    if (it < steps) {
+      const int kc = (warp + GV_WARPS * it) * 128 + t * 16;
+      const uint32_t dst = my_ring_s + (uint32_t)(it % GA_STAGES) * 2048;
+      cp_async16(dst, wa + kc, la && kc < k);
+      cp_async16(dst + 512, wb + kc, lb && kc < k);
+      cp_async16(dst + 1024, wa + kc + 64, la && kc + 64 < k);
+      cp_async16(dst + 1536, wb + kc + 64, lb && kc + 64 < k);
+    }
+    cp_async_commit();     // one group per step, also when it is empty: the wait below counts groups
+  };
+#pragma unroll
+  for (int it = 0; it < GA_STAGES - 1; ++it) issue(it);
+
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint8_t *xcol = X + (size_t)g * ldx * XB;
+  const bool xlive = g < n;
+  for (int it = 0; it < steps; ++it) {
+    issue(it + GA_STAGES - 1);
+    const int kc = (warp + GV_WARPS * it) * 128;
+    uint4 xq[2][XW];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int kk = kc + h * 64 + t * 16;
+#pragma unroll
+      for (int q = 0; q < XW; ++q)
+        xq[h][q] = xlive && kk < k ? __ldg(reinterpret_cast<const uint4 *>(xcol + (size_t)kk * XB) + q) : make_uint4(0, 0, 0, 0);
+    }
+    cp_async_wait<GA_STAGES - 1>();   // all but the newest GA_STAGES - 1 groups are complete: step `it` has landed
+    const uint8_t *slot = my_ring + (size_t)(it % GA_STAGES) * 2048;
+    uint4 wq[2][2];
+    wq[0][0] = *reinterpret_cast<const uint4 *>(slot);
+    wq[0][1] = *reinterpret_cast<const uint4 *>(slot + 512);
+    wq[1][0] = *reinterpret_cast<const uint4 *>(slot + 1024);
+    wq[1][1] = *reinterpret_cast<const uint4 *>(slot + 1536);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t xw[8];
+      if (XT == E5MA_BF16) {
+        xw[0] = xq[h][0].x; xw[1] = xq[h][0].y; xw[2] = xq[h][0].z; xw[3] = xq[h][0].w;
+        xw[4] = xq[h][XW - 1].x; xw[5] = xq[h][XW - 1].y; xw[6] = xq[h][XW - 1].z; xw[7] = xq[h][XW - 1].w;
+      } else {
+        const uint32_t q[4] = {xq[h][0].x, xq[h][0].y, xq[h][0].z, xq[h][0].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) fp8x4_to_bf16x2<XT == E5MA_BF16 ? E5MA_E5M2 : XT>(q[e], xw[2 * e], xw[2 * e + 1]);
+      }
+      const uint32_t qa[4] = {wq[h][0].x, wq[h][0].y, wq[h][0].z, wq[h][0].w};
+      const uint32_t qb[4] = {wq[h][1].x, wq[h][1].y, wq[h][1].z, wq[h][1].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        uint32_t a0, a2, a1, a3;
+        fp8x4_to_bf16x2<AT>(qa[e], a0, a2);   // row g:   k pairs (0,1) and (2,3) of this word
+        fp8x4_to_bf16x2<AT>(qb[e], a1, a3);   // row g+8
+        mma_bf16_16816(acc, a0, a1, a2, a3, xw[2 * e], xw[2 * e + 1]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  red[warp][g][2 * t] = acc[0];
+  red[warp][g][2 * t + 1] = acc[1];
+  red[warp][g + 8][2 * t] = acc[2];
+  red[warp][g + 8][2 * t + 1] = acc[3];
+  __syncthreads();
+  const OutScalars r = out_begin(o);
+  float mx = 0.f;
+  if (threadIdx.x < 128) {
+    const int il = threadIdx.x & 15, j = threadIdx.x >> 4, i = row0 + il;
+    if (i < m && j < n) {
+      float s = red[0][il][j];
+#pragma unroll
+      for (int w = 1; w < GV_WARPS; ++w) s = __fadd_rn(s, red[w][il][j]);
+      mx = out_store(o, r, i, j, s);
+    }
+  }
+  if (o.amax) block_amax(o.amax, mx);
+}
+
+template <int AT, int GA_STAGES>
+static cudaError_t gemv_async_x(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
+                                const OutDesc &o, cudaStream_t s) {
+  constexpr int GA_SMEM = GV_WARPS * GA_STAGES * 2048;
+  const unsigned grid = (unsigned)((m + 15) / 16);
+  static bool attr_done[3][64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+#define E5B_GEMV_CASE(XT, slot_)                                                                                            \
+  {                                                                                                                         \
+    if (!attr_done[slot_][dev & 63]) {                                                                                      \
+      const cudaError_t e = cudaFuncSetAttribute(gemv_async_kernel<AT, XT, GA_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, GA_SMEM); \
+      if (e != cudaSuccess) return e;                                                                                       \
+      attr_done[slot_][dev & 63] = true;                                                                                    \
+    }                                                                                                                       \
+    gemv_async_kernel<AT, XT, GA_STAGES><<<grid, GV_WARPS * 32, GA_SMEM, s>>>(A, lda, X, ldx, m, n, k, o);                             \
+  }
+  switch (x_dtype) {
+    case E5MA_BF16: E5B_GEMV_CASE(E5MA_BF16, 0) break;
+    case E5MA_E5M2: E5B_GEMV_CASE(E5MA_E5M2, 1) break;
+    case E5MA_E4M3: E5B_GEMV_CASE(E5MA_E4M3, 2) break;
+    default: return cudaErrorNotSupported;
+  }
+#undef E5B_GEMV_CASE
+  return cudaGetLastError();
+}
+
 template <int MT, int AT, int U>
 static cudaError_t gemv_xu(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
                            const OutDesc &o, cudaStream_t s) {
@@ -166,6 +305,24 @@ static cudaError_t gemv_x(int x_dtype, const uint8_t *A, int lda, const uint8_t 
 // re-read from L2, which matters once X is no longer tiny next to a block's share of W.
 cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx,
                             int m, int n, int k, const OutDesc &o, int sms, cudaStream_t s) {
+  // Measured on B200 (8192 x 8192 weights): the cp.async pipeline wins for one or two columns (15.1 us
+  // against 16.0 us), the register-load kernel for wider batches (16.5 us against 18.7 us), where X is no
+  // longer served from L1 and its latency sits on the critical path.  E5MA_GEMV_ASYNC=0/1 (experiments) forces one.
+  bool use_async = n <= 2;
+  if (const char *e = getenv("E5MA_GEMV_ASYNC")) use_async = atoi(e) != 0;
+  if (use_async) {
+    int stages = 2;   // 32 KiB per block: every row tile of an 8192-row matrix is resident in one wave
+    if (const char *e = getenv("E5MA_GEMV_STAGES")) stages = atoi(e);
+    if (a_dtype == E5MA_E5M2)
+      return stages == 2 ? gemv_async_x<E5MA_E5M2, 2>(x_dtype, A, lda, X, ldx, m, n, k, o, s)
+           : stages == 4 ? gemv_async_x<E5MA_E5M2, 4>(x_dtype, A, lda, X, ldx, m, n, k, o, s)
+                         : gemv_async_x<E5MA_E5M2, 3>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
+    if (a_dtype == E5MA_E4M3)
+      return stages == 2 ? gemv_async_x<E5MA_E4M3, 2>(x_dtype, A, lda, X, ldx, m, n, k, o, s)
+           : stages == 4 ? gemv_async_x<E5MA_E4M3, 4>(x_dtype, A, lda, X, ldx, m, n, k, o, s)
+                         : gemv_async_x<E5MA_E4M3, 3>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
+    return cudaErrorNotSupported;
+  }
   bool wide = false;   // measured on B200: 16 rows per block wins for every n <= 8 (more blocks, fewer registers)
   (void)sms;
   if (const char *e = getenv("E5MA_GEMV_MT")) wide = atoi(e) == 2;   // experiments
