@@ -49,7 +49,7 @@ template <int BI, int CONV> struct Cfg {
   static constexpr int RAW_ROWS = CONV == 1 ? BI : (CONV == 2 ? BM : 0);
   static constexpr int RAW_BYTES = RAW_ROWS * (STAGE_K_BYTES / 2);   // 64 FP8 bytes per row and k-block
   static constexpr int STAGE_BYTES = J_BYTES + I_BYTES + RAW_BYTES;
-  static constexpr int STAGES = CONV ? (BI == 256 ? 3 : 4) : (BI == 256 ? 4 : 6);
+  static constexpr int STAGES = CONV ? (BI == 256 ? 4 : 5) : (BI == 256 ? 4 : 6);   // mixed: 56 KiB / 40 KiB per stage
   static constexpr int NTHREADS = THREADS;
   static constexpr int TMEM_COLS = 2 * BI;
   // stages + barriers + slack for the 1 KiB alignment of the first stage
@@ -223,15 +223,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int j = j0 + quad * 32 + lane;
+      const int j = j0 + quad * 32 + lane;     // index along the MMA's M side: column j, or row i when transposed
       const bool col_ok = j < n;
-      const float sbj = col_ok && o.sb_vec ? o.sb[j] : sb_const;
+      const float sbj = col_ok && o.sb_vec && !md.transposed ? o.sb[j] : sb_const;
+      float as_i = as_const, bias_i = 0.f;     // transposed: the per-row terms of row i = j
+      if (md.transposed && col_ok) {
+        if (o.sa_vec) as_i = __fmul_rn(o.alpha, o.sa[j]);
+        if (o.bias) bias_i = load_elem(o.bias_dtype, o.bias, (size_t)j, 1.f);
+      }
       const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BI;
       for (int c0 = half * (BI / 2); c0 < (half + 1) * (BI / 2); c0 += 32) {
         if (c0 >= rows || i0 + c0 >= m) break;   // warp-uniform
         float acc[32];
         tmem_ld32(t_lane + c0, acc);
-        if (col_ok) mx = fmaxf(mx, drain32<DT>(o, r, md, acc, i0 + c0, j, m, as_const, sbj));
+        if (col_ok) {
+          if (md.transposed) mx = fmaxf(mx, drain32_t<DT>(o, r, acc, j, i0 + c0, m, as_i, sb_const, bias_i));
+          else mx = fmaxf(mx, drain32<DT>(o, r, md, acc, i0 + c0, j, m, as_const, sbj));
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -302,9 +310,6 @@ static cudaError_t launch_kind(int kind, int conv, int ft, const CUtensorMap &mi
                                const OutDesc &o, const EpiMode &md, int sms, cudaStream_t s) {
   if (kind == 0) return launch_dt<BI, 0, 0, E5MA_E5M2>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
   if (conv == 0) return launch_dt<BI, 1, 0, E5MA_E5M2>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
-  if (conv == 1)
-    return ft == E5MA_E5M2 ? launch_dt<BI, 1, 1, E5MA_E5M2>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s)
-                           : launch_dt<BI, 1, 1, E5MA_E4M3>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
   return ft == E5MA_E5M2 ? launch_dt<BI, 1, 2, E5MA_E5M2>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s)
                          : launch_dt<BI, 1, 2, E5MA_E4M3>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
 }
@@ -339,7 +344,7 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
     const auto vec_ok2 = [](const void *p, int ld, int dtype) {
       return ((uintptr_t)p & 15u) == 0 && ((size_t)ld * elem_bytes(dtype)) % 16 == 0;
     };
-    EpiMode pm;
+    EpiMode pm = {};
     pm.split = 1;
     if (const char *e = getenv("E5MA_TC_SPLIT")) pm.split = atoi(e);
     pm.vec = vec_ok2(o.d, o.ldd, o.d_dtype);
@@ -351,31 +356,41 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
     return f8 ? launch_pair<0>(pi, pj, pi2, pi4, m, n, k * 1, pdesc, ps, o, pm, sms, s)
               : launch_pair<1>(pi, pj, pi2, pi4, m, n, k * 2, pdesc, ps, o, pm, sms, s);
   }
-  const int tiles256 = ((m + 255) / 256) * ((n + BM - 1) / BM);
-  const bool wide = m > 128 && (tiles256 >= sms || m % 256 == 0 || m > 1024);
+  // Mixed pairs widen their FP8 operand in shared memory; that costs least when the FP8 operand sits on the
+  // MMA's M side (128 rows per tile instead of 256).  The M side is op(B)^T, so an FP8 A is handled by
+  // running the kernel on the transposed problem (operands and m / n swapped, transposed epilogue).
+  const bool tr = conv == 1;
+  const uint8_t *pn = tr ? B : A, *pm = tr ? A : B;            // N-side / M-side operand storage
+  const int dn = tr ? b_dtype : a_dtype, dm = tr ? a_dtype : b_dtype;
+  const int ldn = tr ? ldb : lda, ldm = tr ? lda : ldb;
+  const int en = tr ? n : m, em = tr ? m : n;                  // N-side / M-side extents
+  const int kconv = conv ? 2 : 0;                              // after the swap the FP8 operand is always on the M side
+  const int tiles256 = ((en + 255) / 256) * ((em + BM - 1) / BM);
+  const bool wide = en > 128 && (tiles256 >= sms || en % 256 == 0 || en > 1024);
   const int bi = wide ? 256 : 128;
-  CUtensorMap mi, mj, mih;   // mih: op(A) with half-height boxes, for the half tiles of the last round
-  if (!make_map(&mi, A, elem_bytes(a_dtype), k, m, lda, bi, conv == 1) ||
-      !make_map(&mj, B, elem_bytes(b_dtype), k, n, ldb, BM, conv == 2) ||
-      !make_map(&mih, A, elem_bytes(a_dtype), k, m, lda, bi / 2, conv == 1))
+  CUtensorMap mi, mj, mih;   // mih: the N-side operand with half-height boxes, for the half tiles of the last round
+  if (!make_map(&mi, pn, elem_bytes(dn), k, en, ldn, bi, false) ||
+      !make_map(&mj, pm, elem_bytes(dm), k, em, ldm, BM, conv != 0) ||
+      !make_map(&mih, pn, elem_bytes(dn), k, en, ldn, bi / 2, false))
     return cudaErrorNotSupported;
-  // the MMA's A operand (M side) is op(B)^T, its B operand (N side) is op(A)
-  const int fi = f8 ? (a_dtype == E5MA_E5M2 ? 1 : 0) : 1, fj = f8 ? (b_dtype == E5MA_E5M2 ? 1 : 0) : 1;
-  const uint32_t idesc = instr_desc(fj, fi, BM, bi), idesc_half = instr_desc(fj, fi, BM, bi / 2);
+  // operand formats of the instruction: FP8 codes for kind::f8f6f4 (E4M3 = 0, E5M2 = 1), BF16 = 1 for kind::f16
+  const int fn_ = f8 ? (dn == E5MA_E5M2 ? 1 : 0) : 1, fm_ = f8 ? (dm == E5MA_E5M2 ? 1 : 0) : 1;
+  const uint32_t idesc = instr_desc(fm_, fn_, BM, bi), idesc_half = instr_desc(fm_, fn_, BM, bi / 2);
   const int k_bytes = k * (f8 ? 1 : 2);   // bytes of K per operand row as the MMA sees it
   // 16-byte vector access in the epilogue: D (and C, bias) bases and column pitches must allow it
   const auto vec_ok = [](const void *p, int ld, int dtype) {
     return ((uintptr_t)p & 15u) == 0 && ((size_t)ld * elem_bytes(dtype)) % 16 == 0;
   };
-  EpiMode md;
+  EpiMode md = {};
+  md.transposed = tr ? 1 : 0;
   md.split = wide ? 1 : 0;
   if (const char *e = getenv("E5MA_TC_SPLIT")) md.split = atoi(e) && wide;   // experiments
   md.vec = vec_ok(o.d, o.ldd, o.d_dtype);
   if (o.c && !((o.c_dtype == E5MA_FP32 || o.c_dtype == E5MA_BF16) && vec_ok(o.c, o.ldc, o.c_dtype))) md.vec = 0;
   if (o.bias && !((o.bias_dtype == E5MA_FP32 || o.bias_dtype == E5MA_BF16) && ((uintptr_t)o.bias & 15u) == 0)) md.vec = 0;
   if (o.sa_vec && ((uintptr_t)o.sa & 15u)) md.vec = 0;
-  return wide ? launch_kind<256>(kind, conv, ft, mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s)
-              : launch_kind<128>(kind, conv, ft, mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md, sms, s);
+  return wide ? launch_kind<256>(kind, kconv, ft, mi, mj, mih, en, em, k_bytes, idesc, idesc_half, o, md, sms, s)
+              : launch_kind<128>(kind, kconv, ft, mi, mj, mih, en, em, k_bytes, idesc, idesc_half, o, md, sms, s);
 }
 
 }  // namespace e5b

@@ -194,7 +194,9 @@ __device__ __forceinline__ void store32(void *p, const float v[32], float qs) {
 // What the epilogue of one launch needs beyond OutDesc: whether D (and C) admit 16-byte vector
 // access (base and leading dimension multiples of 16 bytes) and whether bias / C have a dtype the
 // vector path reads directly.
-struct EpiMode { int vec; int split; };   // split: the last partial wave of tiles is cut into half tiles
+// split: the last partial wave of tiles is cut into half tiles.  transposed: the kernel was given the
+// operands in swapped roles (TMEM lanes are rows i, TMEM columns are columns j) and its m / n are swapped.
+struct EpiMode { int vec; int split; int transposed; };
 
 // One thread's 32 accumulators: column j, rows ib .. ib+31.  Fast path when the 32 rows are all
 // inside the matrix and vector access is allowed; otherwise element by element.
@@ -244,6 +246,54 @@ __device__ __forceinline__ float drain32(const OutDesc &o, const OutScalars &r, 
         mx = fmaxf(mx, fabsf(v));
         store_out<DT>(o.d, (size_t)j * o.ldd + i, v, r.qs);
       }
+    }
+  }
+  return mx;
+}
+
+// The same for a kernel that ran with swapped operand roles: the thread's TMEM lane is row i, its 32
+// accumulators are columns jb .. jb+31.  Stores of one column by the 32 lanes of a warp are contiguous
+// (32 consecutive i), so plain element stores coalesce; per-row terms were read once by the caller.
+template <int DT>
+__device__ __forceinline__ float drain32_t(const OutDesc &o, const OutScalars &r, float acc[32], int i, int jb, int n,
+                                           float as_i, float sb_const, float bias_i) {
+  float mx = 0.f;
+  // scale, then bias
+  if (o.sb_vec) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) acc[e] = __fmul_rn(acc[e], __fmul_rn(as_i, jb + e < n ? o.sb[jb + e] : 0.f));
+  } else {
+    const float s = o.sa_vec ? __fmul_rn(as_i, sb_const) : r.s;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) acc[e] = __fmul_rn(acc[e], s);
+  }
+  if (o.bias) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) acc[e] = __fadd_rn(acc[e], bias_i);
+  }
+  // beta * C: all 32 loads are issued before the first is used
+  if (o.c) {
+    float c[32];
+    if (o.c_dtype == E5MA_FP32) {
+      const float *cp = (const float *)o.c + (size_t)jb * o.ldc + i;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) c[e] = jb + e < n ? cp[(size_t)e * o.ldc] : 0.f;
+    } else if (o.c_dtype == E5MA_BF16) {
+      const uint16_t *cp = (const uint16_t *)o.c + (size_t)jb * o.ldc + i;
+#pragma unroll
+      for (int e = 0; e < 32; ++e) c[e] = jb + e < n ? dec_bf16(cp[(size_t)e * o.ldc]) : 0.f;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) c[e] = jb + e < n ? load_elem(o.c_dtype, o.c, (size_t)(jb + e) * o.ldc + i, r.csinv) : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 32; ++e) acc[e] = __fmaf_rn(o.beta, c[e], acc[e]);
+  }
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    if (jb + e < n) {
+      mx = fmaxf(mx, fabsf(acc[e]));
+      store_out<DT>(o.d, (size_t)(jb + e) * o.ldd + i, acc[e], r.qs);
     }
   }
   return mx;
