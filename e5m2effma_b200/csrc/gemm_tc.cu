@@ -136,8 +136,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
           // coordinates are in elements of the tensor map: the innermost one counts bytes for FP8 and
           // 2-byte elements for BF16; a k-block is 128 FP8 or 64 BF16 (and then also 64 raw FP8) elements
           const int kc = kb * (KIND == 0 ? STAGE_K_BYTES : STAGE_K_BYTES / 2);
-          tma_load_2d(CONV == 2 ? sraw : sj, &map_j, kc, j0, full_bar(s));
-          tma_load_2d(CONV == 1 ? sraw : si, half_tile ? &map_ih : &map_i, kc, i0, full_bar(s));
+          // K-major operand: one box of all its rows.  MN-major operand: one box per 128 bytes of rows (each
+          // box is a full stage of k-rows x 128 bytes), the boxes lie MN_BOX_BYTES apart.
+          constexpr int EB = KIND == 0 ? 1 : 2, MN_BOX_BYTES = (STAGE_K_BYTES / EB) * 128;
+          if (CONV == 0 && md.mn_m) {
+            for (int b = 0; b < BM * EB / 128; ++b) tma_load_2d(sj + b * MN_BOX_BYTES, &map_j, j0 + b * (128 / EB), kc, full_bar(s));
+          } else {
+            tma_load_2d(CONV == 2 ? sraw : sj, &map_j, kc, j0, full_bar(s));
+          }
+          if (CONV == 0 && md.mn_n) {
+            for (int b = 0; b < rows * EB / 128; ++b) tma_load_2d(si + b * MN_BOX_BYTES, &map_i, i0 + b * (128 / EB), kc, full_bar(s));
+          } else {
+            tma_load_2d(CONV == 1 ? sraw : si, half_tile ? &map_ih : &map_i, kc, i0, full_bar(s));
+          }
         }
       }
     }
@@ -161,12 +172,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
           if (CONV && !mbar_wait(ready_bar(s), ph, abort_flag, (4u << 24) | (uint32_t)kb)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sj = ring + s * C::STAGE_BYTES, si = sj + C::J_BYTES;
-          const uint64_t dj = kmajor_sw128_desc(sj), di = kmajor_sw128_desc(si);
+          // K-major: stepping 32 bytes along K inside the swizzled row = +2 in the 16-byte address field.
+          // MN-major: one MMA spans 32 bytes of K = 32 (FP8) or 16 (BF16) k-rows of 128 bytes = +256 / +128.
+          constexpr int EB = KIND == 0 ? 1 : 2;
+          constexpr uint32_t MN_BOX_BYTES = (STAGE_K_BYTES / EB) * 128, MN_STEP = (MMA_K_BYTES / EB) * 128 / 16;
+          const bool mnj = CONV == 0 && md.mn_m, mni = CONV == 0 && md.mn_n;
+          const uint64_t dj = mnj ? mnmajor_sw128_desc(sj, MN_BOX_BYTES) : kmajor_sw128_desc(sj);
+          const uint64_t di = mni ? mnmajor_sw128_desc(si, MN_BOX_BYTES) : kmajor_sw128_desc(si);
+          const uint32_t stepj = mnj ? MN_STEP : 2u, stepi = mni ? MN_STEP : 2u;
 #pragma unroll
-          for (int ks = 0; ks < STAGE_K_BYTES / MMA_K_BYTES; ++ks) {
-            // stepping 32 bytes along K inside the swizzled row = +2 in the 16-byte address field
-            mma_ss<KIND>(d_tmem, dj + 2u * ks, di + 2u * ks, idesc_t, (kb | ks) != 0);
-          }
+          for (int ks = 0; ks < STAGE_K_BYTES / MMA_K_BYTES; ++ks)
+            mma_ss<KIND>(d_tmem, dj + stepj * ks, di + stepi * ks, idesc_t, (kb | ks) != 0);
           mma_commit(empty_bar(s));
         }
         if (ok) mma_commit(acc_full(buf));
@@ -324,16 +340,19 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
                            const uint8_t *B, int ldb, int m, int n, int k, const OutDesc &o, int sms,
                            cudaStream_t s) {
   using namespace tc;
-  if (!a_kc || !b_kc || k <= 0) return cudaErrorNotSupported;
+  if (k <= 0) return cudaErrorNotSupported;
   if (a_dtype == E5MA_FP32 || b_dtype == E5MA_FP32) return cudaErrorNotSupported;
   const bool f8 = is_fp8(a_dtype) && is_fp8(b_dtype);
   const int conv = f8 ? 0 : (is_fp8(a_dtype) ? 1 : (is_fp8(b_dtype) ? 2 : 0));
+  // operands stored contiguous along m / n (transa = N, transb = T) are read as MN-major MMA operands; the
+  // mixed pairs (which rewrite an operand in shared memory) and the CTA-pair kernel take K-contiguous ones only
+  if ((!a_kc || !b_kc) && conv != 0) return cudaErrorNotSupported;
   const int kind = f8 ? 0 : 1;
   const int ft = conv == 1 ? a_dtype : (conv == 2 ? b_dtype : E5MA_E5M2);
   // CTA pairs (gemm_tc2.cuh) for big unmixed problems: 256 x 256 tiles, half the operand bytes per CTA
   int use_pair = 1;
   if (const char *e = getenv("E5MA_TC_PAIR")) use_pair = atoi(e);   // experiments: 0 keeps every problem on single CTAs
-  if (use_pair && conv == 0 && m >= 512 && n >= 512 && ((m + 255) / 256) * ((n + 255) / 256) >= sms / 2) {
+  if (use_pair && a_kc && b_kc && conv == 0 && m >= 512 && n >= 512 && ((m + 255) / 256) * ((n + 255) / 256) >= sms / 2) {
     CUtensorMap pi, pj, pi2, pi4;
     if (!make_map(&pi, A, elem_bytes(a_dtype), k, m, lda, 128, false) ||
         !make_map(&pj, B, elem_bytes(b_dtype), k, n, ldb, 128, false) ||
@@ -369,13 +388,14 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   const bool wide = en > 128 && (tiles256 >= sms || en % 256 == 0 || en > 1024);
   const int bi = wide ? 256 : 128;
   CUtensorMap mi, mj, mih;   // mih: the N-side operand with half-height boxes, for the half tiles of the last round
-  if (!make_map(&mi, pn, elem_bytes(dn), k, en, ldn, bi, false) ||
-      !make_map(&mj, pm, elem_bytes(dm), k, em, ldm, BM, conv != 0) ||
-      !make_map(&mih, pn, elem_bytes(dn), k, en, ldn, bi / 2, false))
+  const bool n_kc = tr ? b_kc : a_kc, m_kc = tr ? a_kc : b_kc;   // storage of the N-side / M-side operand
+  if (!(n_kc ? make_map(&mi, pn, elem_bytes(dn), k, en, ldn, bi, false) : make_map_mn(&mi, pn, elem_bytes(dn), k, en, ldn)) ||
+      !(m_kc ? make_map(&mj, pm, elem_bytes(dm), k, em, ldm, BM, conv != 0) : make_map_mn(&mj, pm, elem_bytes(dm), k, em, ldm)) ||
+      !(n_kc ? make_map(&mih, pn, elem_bytes(dn), k, en, ldn, bi / 2, false) : make_map_mn(&mih, pn, elem_bytes(dn), k, en, ldn)))
     return cudaErrorNotSupported;
   // operand formats of the instruction: FP8 codes for kind::f8f6f4 (E4M3 = 0, E5M2 = 1), BF16 = 1 for kind::f16
   const int fn_ = f8 ? (dn == E5MA_E5M2 ? 1 : 0) : 1, fm_ = f8 ? (dm == E5MA_E5M2 ? 1 : 0) : 1;
-  const uint32_t idesc = instr_desc(fm_, fn_, BM, bi), idesc_half = instr_desc(fm_, fn_, BM, bi / 2);
+  const uint32_t idesc = instr_desc(fm_, fn_, BM, bi, !m_kc, !n_kc), idesc_half = instr_desc(fm_, fn_, BM, bi / 2, !m_kc, !n_kc);
   const int k_bytes = k * (f8 ? 1 : 2);   // bytes of K per operand row as the MMA sees it
   // 16-byte vector access in the epilogue: D (and C, bias) bases and column pitches must allow it
   const auto vec_ok = [](const void *p, int ld, int dtype) {
@@ -383,6 +403,8 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   };
   EpiMode md = {};
   md.transposed = tr ? 1 : 0;
+  md.mn_n = n_kc ? 0 : 1;
+  md.mn_m = m_kc ? 0 : 1;
   md.split = wide ? 1 : 0;
   if (const char *e = getenv("E5MA_TC_SPLIT")) md.split = atoi(e) && wide;   // experiments
   md.vec = vec_ok(o.d, o.ldd, o.d_dtype);

@@ -124,11 +124,20 @@ __device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
+// The same for an MN-major tile (the operand is contiguous along its row index, e.g. op(A) stored m x k):
+// TMA boxes of 128 bytes of MN x R k-rows land as R rows of 128 bytes with the 128-byte swizzle; a tile wider
+// than 128 bytes of MN is several such boxes, lbo_bytes apart (leading offset); groups of 8 k-rows are
+// 1024 bytes apart (stride offset).
+__device__ __forceinline__ uint64_t mnmajor_sw128_desc(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
 // Instruction descriptor: FP32 accumulator (bits 4-5 = 1), operand formats at bits 7-9 / 10-12,
-// both operands K-major (bits 15, 16 = 0), N / 8 at bits 17-22, M / 16 at bits 24-28.
-__host__ __device__ constexpr uint32_t instr_desc(int fmt_a, int fmt_b, int mdim, int ndim) {
-  return (1u << 4) | ((uint32_t)fmt_a << 7) | ((uint32_t)fmt_b << 10) | ((uint32_t)(ndim >> 3) << 17) |
-         ((uint32_t)(mdim >> 4) << 24);
+// bits 15 / 16 = 1 when operand A / B is MN-major (0: K-major), N / 8 at bits 17-22, M / 16 at bits 24-28.
+__host__ __device__ constexpr uint32_t instr_desc(int fmt_a, int fmt_b, int mdim, int ndim, int a_mn = 0, int b_mn = 0) {
+  return (1u << 4) | ((uint32_t)fmt_a << 7) | ((uint32_t)fmt_b << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+         ((uint32_t)(ndim >> 3) << 17) | ((uint32_t)(mdim >> 4) << 24);
 }
 
 // ---- epilogue --------------------------------------------------------------------------------
@@ -196,7 +205,7 @@ __device__ __forceinline__ void store32(void *p, const float v[32], float qs) {
 // vector path reads directly.
 // split: the last partial wave of tiles is cut into half tiles.  transposed: the kernel was given the
 // operands in swapped roles (TMEM lanes are rows i, TMEM columns are columns j) and its m / n are swapped.
-struct EpiMode { int vec; int split; int transposed; };
+struct EpiMode { int vec; int split; int transposed; int mn_n; int mn_m; };   // mn_n / mn_m: the N-side / M-side operand is stored MN-contiguous
 
 // One thread's 32 accumulators: column j, rows ib .. ib+31.  Fast path when the 32 rows are all
 // inside the matrix and vector access is allowed; otherwise element by element.
@@ -319,6 +328,21 @@ inline EncodeTiledFn encode_fn() {
 // K-major operand: rows x k elements, row pitch ld elements.  Operands the MMA reads directly get
 // boxes of 128 bytes of K x box_rows rows with the 128-byte swizzle; an FP8 operand that is widened
 // in shared memory first (raw) gets plain 64-byte rows.
+// MN-contiguous operand (rows x k elements stored k x rows... i.e. element (r, kk) at r + kk * ld): boxes of
+// 128 bytes of rows x one stage of k (128 FP8 / 64 BF16 k-rows), 128-byte swizzle.
+inline bool make_map_mn(CUtensorMap *map, const void *base, int elem_bytes, int k, int rows, int ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)rows, (cuuint64_t)k};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)(STAGE_K_BYTES / elem_bytes)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  return fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+         CUDA_SUCCESS;
+}
+
 inline bool make_map(CUtensorMap *map, const void *base, int elem_bytes, int k, int rows, int ld, int box_rows, bool raw) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
