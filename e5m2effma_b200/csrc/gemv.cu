@@ -186,13 +186,12 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_async_kernel(const uint8_t
 #pragma unroll
   for (int it = 0; it < GA_STAGES - 1; ++it) issue(it);
 
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  // two accumulator sets: consecutive MMAs do not wait on each other's result
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
   const uint8_t *xcol = X + (size_t)g * ldx * XB;
   const bool xlive = g < n;
-  for (int it = 0; it < steps; ++it) {
-    issue(it + GA_STAGES - 1);
+  const auto load_x = [&](int it, uint4 (&xq)[2][XW]) {
     const int kc = (warp + GV_WARPS * it) * 128;
-    uint4 xq[2][XW];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int kk = kc + h * 64 + t * 16;
@@ -200,6 +199,12 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_async_kernel(const uint8_t
       for (int q = 0; q < XW; ++q)
         xq[h][q] = xlive && kk < k ? __ldg(reinterpret_cast<const uint4 *>(xcol + (size_t)kk * XB) + q) : make_uint4(0, 0, 0, 0);
     }
+  };
+  uint4 xq[2][XW], xn[2][XW];
+  load_x(0, xq);
+  for (int it = 0; it < steps; ++it) {
+    issue(it + GA_STAGES - 1);
+    load_x(it + 1, xn);               // X of the next step is fetched while this one is consumed (zeros beyond k)
     cp_async_wait<GA_STAGES - 1>();   // all but the newest GA_STAGES - 1 groups are complete: step `it` has landed
     const uint8_t *slot = my_ring + (size_t)(it % GA_STAGES) * 2048;
     uint4 wq[2][2];
@@ -225,10 +230,16 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_async_kernel(const uint8_t
         uint32_t a0, a2, a1, a3;
         fp8x4_to_bf16x2<AT>(qa[e], a0, a2);   // row g:   k pairs (0,1) and (2,3) of this word
         fp8x4_to_bf16x2<AT>(qb[e], a1, a3);   // row g+8
-        mma_bf16_16816(acc, a0, a1, a2, a3, xw[2 * e], xw[2 * e + 1]);
+        mma_bf16_16816((e & 1) ? acc2 : acc, a0, a1, a2, a3, xw[2 * e], xw[2 * e + 1]);
       }
     }
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int q = 0; q < XW; ++q) xq[h][q] = xn[h][q];
   }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) acc[e] = __fadd_rn(acc[e], acc2[e]);
   cp_async_wait<0>();
 
   red[warp][g][2 * t] = acc[0];
@@ -305,10 +316,10 @@ static cudaError_t gemv_x(int x_dtype, const uint8_t *A, int lda, const uint8_t 
 // re-read from L2, which matters once X is no longer tiny next to a block's share of W.
 cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx,
                             int m, int n, int k, const OutDesc &o, int sms, cudaStream_t s) {
-  // Measured on B200 (8192 x 8192 weights): the cp.async pipeline wins for one or two columns (15.1 us
-  // against 16.0 us), the register-load kernel for wider batches (16.5 us against 18.7 us), where X is no
-  // longer served from L1 and its latency sits on the critical path.  E5MA_GEMV_ASYNC=0/1 (experiments) forces one.
-  bool use_async = n <= 2;
+  // Measured on B200 (8192 x 8192 weights, batch 1 / 8): the cp.async pipeline with X prefetched one step
+  // ahead takes 15.2 / 15.8 us, the register-load kernel 15.8 / 16.6 us.  E5MA_GEMV_ASYNC=0 (experiments)
+  // selects the latter.
+  bool use_async = true;
   if (const char *e = getenv("E5MA_GEMV_ASYNC")) use_async = atoi(e) != 0;
   if (use_async) {
     int stages = 2;   // 32 KiB per block: every row tile of an 8192-row matrix is resident in one wave
