@@ -150,6 +150,41 @@ def cpu_sample(name, target_s=12.0):
     return cnt * es[2] / t1 / 1e9, "GB/s", f"2^27 elements: {t1:.2f} s"
 
 
+def parity_sample(w, orc):
+    """Part of the cpu_baseline leg: the oracle re-computes a few output columns (all rows, full k) of the
+    result the GPU just produced and reports the largest error in units of the stated bound
+    (1 ulp of the output format is allowed on top: a ratio <= 1 is inside the bound without it)."""
+    import numpy as np
+    import torch
+    st = {0: np.uint8, 4: np.uint8, 1: np.uint16, 2: np.uint16, 3: np.float32}
+
+    def host(t):
+        return t.detach().cpu().contiguous().view(torch.uint8).numpy()
+
+    w.launch(torch.cuda.current_stream().cuda_stream)      # a fresh result from the original operands
+    torch.cuda.synchronize()
+    A, B = host(w.A).view(st[w.a_dtype]).reshape(-1), host(w.B).view(st[w.b_dtype]).reshape(-1)
+    D = host(w.D).view(st[w.d_dtype]).reshape(w.n, w.m)
+    if w.beta != 0.0:
+        return {"skipped": "accumulating workload: the timed steps have already changed D"}
+    qs = float(w.d_scale.item()) if w.d_scale is not None else 1.0
+    cols = [(0, min(4, w.n)), (max(0, w.n // 2 - 2), min(w.n, w.n // 2 + 2))] if w.n > 8 else [(0, w.n)]
+    worst = 0.0
+    for j0, j1 in cols:
+        ref, mag, fix = orc.gemm_wide(1, 0, w.m, w.n, w.k, 1.0, A, w.a_dtype, w.k, B, w.b_dtype, w.k, 0.0, None, w.d_dtype, w.m,
+                                      bias=None if w.bias is None else host(w.bias).view(np.uint16), bias_dtype=orc.BF16,
+                                      a_sinv=None if w.sa is None else w.sa.cpu().numpy(), a_outer=w.a_outer,
+                                      b_sinv=None if w.sb is None else w.sb.cpu().numpy(), b_outer=w.b_outer, cols=(j0, j1))
+        got = orc.decode(w.d_dtype, D[j0:j1].copy(), 1.0).astype(np.float64) / qs
+        # one ulp of the output format around the reference, then the accumulation-order bound
+        ulp = {0: 2.0 ** -3, 4: 2.0 ** -2, 1: 2.0 ** -7, 2: 2.0 ** -10, 3: 2.0 ** -23}[w.d_dtype] * np.maximum(np.abs(ref), 1e-30)
+        bound = w.k * 2.0 ** -23 * mag + 2.0 ** -21 * (np.abs(ref) + fix + mag)
+        excess = np.maximum(np.abs(got - ref) - ulp, 0.0) / np.maximum(bound, 1e-300)
+        worst = max(worst, float(excess.max()))
+    return {"columns": sum(b - a for a, b in cols), "rows": w.m, "bound": "k * 2^-23 * sum|a*b|*|s| beyond 1 ulp of the output format",
+            "max_error_over_bound": worst, "ok": worst <= 1.0}
+
+
 def run_reference(args, metric, unit, config):
     """The reference's CPU algorithm (oracle port) on this configuration, all host threads."""
     rank = int(os.environ.get("RANK", "0"))
@@ -416,6 +451,8 @@ def main():
         import oracle as orc
         v, u, sample = cpu_sample(name)
         cpu = {"value": v, "unit": u, "cores": orc.threads(), "kind": "port", "sample": sample}
+        if w.kind == "gemm":
+            cpu["parity_sample"] = parity_sample(w, orc)
 
     line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

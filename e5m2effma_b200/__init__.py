@@ -8,7 +8,7 @@ memory and streams only.  There is no CPU path and no alternative backend: a mis
 a GPU other than compute capability 10.0 raises.
 """
 from . import capi
-from .functional import AdamW, adam_step, cast, get_include, linear, matmul
+from .functional import AdamW, adam_step, adam_step_multi, cast, get_include, linear, matmul
 
 __version__ = "0.2.0"
-__all__ = ["capi", "matmul", "linear", "cast", "adam_step", "AdamW", "get_include", "__version__"]
+__all__ = ["capi", "matmul", "linear", "cast", "adam_step", "adam_step_multi", "AdamW", "get_include", "__version__"]

@@ -49,6 +49,9 @@ def _load():
     lib.e5ma_last_error.argtypes = []
     lib.e5b_gemm_fault.restype = ctypes.c_uint
     lib.e5b_gemm_fault.argtypes = []
+    lib.e5b_adam_multi.restype = ctypes.c_int
+    lib.e5b_adam_multi.argtypes = [ctypes.POINTER(AdamConfig), ctypes.c_int, ctypes.POINTER(ctypes.c_size_t), tp, tp, tp, tp, tp,
+                                   ctypes.c_void_p]
     return lib
 
 
@@ -90,3 +93,14 @@ def cast(src, dst, count, stream=0):
 def adam(cfg, count, param, grad, exp_avg, exp_avg_sq, param_fp8=None, stream=0):
     return lib.e5ma_adam(None if cfg is None else ctypes.byref(cfg), count, _ref(param), _ref(grad), _ref(exp_avg),
                          _ref(exp_avg_sq), _ref(param_fp8), stream)
+
+
+def adam_multi(cfg, counts, params, grads, exp_avgs, exp_avg_sqs, params_fp8=None, stream=0):
+    """e5b_adam_multi: lists of capi.Tensor of equal length (params_fp8: None or a list whose entries may
+    have data = None for "no copy"... all entries must then agree); returns the e5ma_status."""
+    n = len(counts)
+    arr = lambda ts: (Tensor * n)(*ts) if n else (Tensor * 1)()
+    c = (ctypes.c_size_t * max(n, 1))(*counts)
+    q = None if params_fp8 is None else arr(params_fp8)
+    return lib.e5b_adam_multi(None if cfg is None else ctypes.byref(cfg), n, c, arr(params), arr(grads), arr(exp_avgs),
+                              arr(exp_avg_sqs), q, stream)

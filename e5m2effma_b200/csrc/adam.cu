@@ -10,6 +10,7 @@
 // read p, g, m, v (8 B) + write p, m, v (6 B) + write q (1 B) = 15 B.
 #include <math.h>
 #include "common.cuh"
+#include "../../include/e5m2effma_b200.h"
 
 namespace e5b {
 
@@ -62,14 +63,13 @@ __device__ __forceinline__ void store8(void *base, size_t i, const float x[8]) {
 // QT dtype of the FP8 copy or -1 for none.  VEC: all pointers 16-byte aligned (the copy 8-byte);
 // then groups of 8 elements use vector accesses and only count % 8 trailing elements go one by one.
 // Both paths evaluate adam_update, so an element's result does not depend on the path.
+// Elements [0, count) of one tensor, spread over nthr threads of which this is number tid: groups of 8
+// elements with vector accesses when VEC, the rest one by one.  Returns the thread's max |p| (FP8 copy only).
 template <int PT, int GT, int MT, int QT, bool VEC>
-__global__ void __launch_bounds__(256) adam_kernel(AdamScalars a, size_t count, void *__restrict__ p_,
-                                                   const void *__restrict__ g_, void *__restrict__ m_,
-                                                   void *__restrict__ v_, uint8_t *__restrict__ q_,
-                                                   const float *qscale_p, float *amax) {
-  const float qs = QT != -1 ? ld_or_one(qscale_p) : 1.f;
+__device__ __forceinline__ float adam_range(const AdamScalars &a, size_t count, void *__restrict__ p_,
+                                            const void *__restrict__ g_, void *__restrict__ m_, void *__restrict__ v_,
+                                            uint8_t *__restrict__ q_, float qs, size_t tid, size_t nthr) {
   float mx = 0.f;
-  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (size_t)gridDim.x * blockDim.x;
   const size_t groups = VEC ? count / 8 : 0;
   for (size_t gi = tid; gi < groups; gi += nthr) {
     const size_t i = gi * 8;
@@ -102,7 +102,51 @@ __global__ void __launch_bounds__(256) adam_kernel(AdamScalars a, size_t count, 
       mx = fmaxf(mx, fabsf(p));
     }
   }
+  return mx;
+}
+
+template <int PT, int GT, int MT, int QT, bool VEC>
+__global__ void __launch_bounds__(256) adam_kernel(AdamScalars a, size_t count, void *__restrict__ p_,
+                                                   const void *__restrict__ g_, void *__restrict__ m_,
+                                                   void *__restrict__ v_, uint8_t *__restrict__ q_,
+                                                   const float *qscale_p, float *amax) {
+  const float qs = QT != -1 ? ld_or_one(qscale_p) : 1.f;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (size_t)gridDim.x * blockDim.x;
+  const float mx = adam_range<PT, GT, MT, QT, VEC>(a, count, p_, g_, m_, v_, q_, qs, tid, nthr);
   if (QT != -1 && amax) block_amax(amax, mx);
+}
+
+// ---- several tensors per launch ------------------------------------------------------------------
+// The table travels by value in the kernel parameters (no device-side table to allocate or copy).  Every
+// block owns one chunk of MT_CHUNK elements of one tensor; first_block[t] is the number of the first block
+// of tensor t, so a block finds its tensor by a short scan.
+constexpr int MT_MAX = 24;
+constexpr size_t MT_CHUNK = 256 * 8 * 8;
+struct AdamTable {
+  void *p[MT_MAX]; const void *g[MT_MAX]; void *m[MT_MAX]; void *v[MT_MAX]; uint8_t *q[MT_MAX];
+  const float *qs[MT_MAX]; float *amax[MT_MAX];
+  size_t count[MT_MAX];
+  unsigned first_block[MT_MAX + 1];
+  unsigned char vec[MT_MAX];
+  int n;
+};
+
+template <int PT, int GT, int MT, int QT>
+__global__ void __launch_bounds__(256) adam_multi_kernel(AdamScalars a, const __grid_constant__ AdamTable tb) {
+  int t = 0;
+  while (t + 1 < tb.n && blockIdx.x >= tb.first_block[t + 1]) ++t;
+  const size_t begin = (size_t)(blockIdx.x - tb.first_block[t]) * MT_CHUNK;
+  const size_t len = tb.count[t] - begin < MT_CHUNK ? tb.count[t] - begin : MT_CHUNK;
+  constexpr int PB = elem_bytes(PT), GB = elem_bytes(GT), MB = elem_bytes(MT);
+  void *p_ = (uint8_t *)tb.p[t] + begin * PB;
+  const void *g_ = (const uint8_t *)tb.g[t] + begin * GB;
+  void *m_ = (uint8_t *)tb.m[t] + begin * MB, *v_ = (uint8_t *)tb.v[t] + begin * MB;
+  uint8_t *q_ = QT != -1 ? tb.q[t] + begin : nullptr;
+  const float qs = QT != -1 ? ld_or_one(tb.qs[t]) : 1.f;
+  float mx;   // chunk starts are multiples of 16384 elements, so a tensor's alignment carries over to its chunks
+  if (tb.vec[t]) mx = adam_range<PT, GT, MT, QT, true>(a, len, p_, g_, m_, v_, q_, qs, threadIdx.x, 256);
+  else mx = adam_range<PT, GT, MT, QT, false>(a, len, p_, g_, m_, v_, q_, qs, threadIdx.x, 256);
+  if (QT != -1 && tb.amax[t]) block_amax(tb.amax[t], mx);
 }
 
 struct AdamPtrs { void *p; const void *g; void *m, *v; uint8_t *q; const float *qs; float *amax; };
@@ -188,4 +232,104 @@ extern "C" e5ma_status e5ma_adam(const e5ma_adam_config *cfg, size_t count, cons
                               ? adam_g<E5MA_BF16>(grad->dtype, exp_avg->dtype, qt, a, count, x, dp.sms, stream)
                               : adam_g<E5MA_FP32>(grad->dtype, exp_avg->dtype, qt, a, count, x, dp.sms, stream);
   return cuda_fail(err, "e5ma_adam: kernel launch");
+}
+
+namespace e5b {
+template <int PT, int GT, int MT>
+static cudaError_t adam_multi_q(int qt, bool copy, const AdamScalars &a, const AdamTable &tb, unsigned blocks, cudaStream_t s) {
+  if (!copy) adam_multi_kernel<PT, GT, MT, -1><<<blocks, 256, 0, s>>>(a, tb);
+  else if (qt == E5MA_E5M2) adam_multi_kernel<PT, GT, MT, E5MA_E5M2><<<blocks, 256, 0, s>>>(a, tb);
+  else adam_multi_kernel<PT, GT, MT, E5MA_E4M3><<<blocks, 256, 0, s>>>(a, tb);
+  return cudaGetLastError();
+}
+template <int PT, int GT>
+static cudaError_t adam_multi_m(int mt, int qt, bool copy, const AdamScalars &a, const AdamTable &tb, unsigned blocks, cudaStream_t s) {
+  return mt == E5MA_BF16 ? adam_multi_q<PT, GT, E5MA_BF16>(qt, copy, a, tb, blocks, s)
+                         : adam_multi_q<PT, GT, E5MA_FP32>(qt, copy, a, tb, blocks, s);
+}
+template <int PT>
+static cudaError_t adam_multi_g(int gt, int mt, int qt, bool copy, const AdamScalars &a, const AdamTable &tb, unsigned blocks, cudaStream_t s) {
+  if (gt == E5MA_BF16) return adam_multi_m<PT, E5MA_BF16>(mt, qt, copy, a, tb, blocks, s);
+  if (gt == E5MA_FP16) return adam_multi_m<PT, E5MA_FP16>(mt, qt, copy, a, tb, blocks, s);
+  return adam_multi_m<PT, E5MA_FP32>(mt, qt, copy, a, tb, blocks, s);
+}
+}  // namespace e5b
+
+extern "C" e5ma_status e5b_adam_multi(const e5ma_adam_config *cfg, int num_tensors, const size_t *counts,
+                                      const e5ma_tensor *params, const e5ma_tensor *grads, const e5ma_tensor *exp_avgs,
+                                      const e5ma_tensor *exp_avg_sqs, const e5ma_tensor *params_fp8, cudaStream_t stream) {
+  using namespace e5b;
+  clear_error();
+  if (!cfg || !counts || !params || !grads || !exp_avgs || !exp_avg_sqs)
+    return fail(E5MA_INVALID_VALUE, "e5b_adam_multi: cfg, counts or a tensor list is NULL");
+  if (num_tensors < 0) return fail(E5MA_INVALID_VALUE, "e5b_adam_multi: num_tensors = %d", num_tensors);
+  if (cfg->step < 1) return fail(E5MA_INVALID_VALUE, "e5b_adam_multi: step = %d, must be >= 1", cfg->step);
+  const auto state_type = [](int t) { return t == E5MA_FP32 || t == E5MA_BF16; };
+  bool any = false, copy = false;
+  int pt = 0, gt = 0, mt = 0, qt = E5MA_E4M3;
+  for (int t = 0; t < num_tensors; ++t) {
+    if (!params[t].data || !grads[t].data || !exp_avgs[t].data || !exp_avg_sqs[t].data)
+      return fail(E5MA_INVALID_VALUE, "e5b_adam_multi: tensor %d has a NULL data pointer", t);
+    if (!state_type(params[t].dtype))
+      return fail(E5MA_NOT_SUPPORTED, "e5b_adam_multi: param %d must be FP32 or BF16 (dtype %d)", t, (int)params[t].dtype);
+    if (!state_type(exp_avgs[t].dtype) || exp_avg_sqs[t].dtype != exp_avgs[t].dtype)
+      return fail(E5MA_NOT_SUPPORTED, "e5b_adam_multi: moments of tensor %d must both be FP32 or both BF16", t);
+    if (grads[t].dtype != E5MA_FP32 && grads[t].dtype != E5MA_BF16 && grads[t].dtype != E5MA_FP16)
+      return fail(E5MA_NOT_SUPPORTED, "e5b_adam_multi: grad %d must be FP32, BF16 or FP16 (dtype %d)", t, (int)grads[t].dtype);
+    const bool c = params_fp8 && params_fp8[t].data;
+    if (c && !is_fp8(params_fp8[t].dtype))
+      return fail(E5MA_INVALID_VALUE, "e5b_adam_multi: param_fp8 %d must be E4M3 or E5M2 (dtype %d)", t, (int)params_fp8[t].dtype);
+    if (c && params_fp8[t].scaling != E5MA_SCALING_TENSOR)
+      return fail(E5MA_INVALID_VALUE, "e5b_adam_multi: param_fp8 takes per-tensor scaling only");
+    if (!any) { pt = params[t].dtype; gt = grads[t].dtype; mt = exp_avgs[t].dtype; copy = c; qt = c ? (int)params_fp8[t].dtype : qt; any = true; }
+    else if (pt != (int)params[t].dtype || gt != (int)grads[t].dtype || mt != (int)exp_avgs[t].dtype || copy != c ||
+             (c && qt != (int)params_fp8[t].dtype))
+      return fail(E5MA_INVALID_VALUE, "e5b_adam_multi: tensor %d differs in dtype (or in having an FP8 copy) from tensor 0; "
+                  "group tensors of one kind per call", t);
+  }
+  if (!any) return E5MA_OK;
+  DeviceProps dp;
+  if (e5ma_status st = require_blackwell("e5b_adam_multi", &dp)) return st;
+
+  AdamScalars a;
+  a.lr = cfg->lr; a.beta1 = cfg->beta1; a.beta2 = cfg->beta2; a.eps = cfg->eps; a.wd = cfg->weight_decay;
+  a.omb1 = (float)(1.0 - (double)cfg->beta1);
+  a.omb2 = (float)(1.0 - (double)cfg->beta2);
+  a.rbc1 = cfg->bias_correction ? (float)(1.0 / (1.0 - pow((double)cfg->beta1, cfg->step))) : 1.f;
+  a.rbc2 = cfg->bias_correction ? (float)(1.0 / (1.0 - pow((double)cfg->beta2, cfg->step))) : 1.f;
+  a.lr_wd = (float)((double)cfg->lr * cfg->weight_decay);
+  a.gscale = cfg->grad_scale == 0.f ? 1.f : cfg->grad_scale;
+  a.adamw = cfg->adamw;
+
+  const auto a16 = [](const void *p) { return ((uintptr_t)p & 15u) == 0; };
+  int t = 0;
+  while (t < num_tensors) {   // one launch per MT_MAX non-empty tensors
+    AdamTable tb;
+    tb.n = 0;
+    unsigned blocks = 0;
+    for (; t < num_tensors && tb.n < MT_MAX; ++t) {
+      if (counts[t] == 0) continue;
+      const size_t nb = (counts[t] + MT_CHUNK - 1) / MT_CHUNK;
+      if (nb > 0x7FFFFFFFu - blocks) break;   // keeps the grid inside 2^31 - 1 blocks; the rest goes to the next launch
+      const int e = tb.n++;
+      tb.p[e] = params[t].data; tb.g[e] = grads[t].data; tb.m[e] = exp_avgs[t].data; tb.v[e] = exp_avg_sqs[t].data;
+      tb.q[e] = copy ? (uint8_t *)params_fp8[t].data : nullptr;
+      tb.qs[e] = copy ? params_fp8[t].scale : nullptr;
+      tb.amax[e] = copy ? params_fp8[t].amax : nullptr;
+      tb.count[e] = counts[t];
+      tb.first_block[e] = blocks;
+      tb.vec[e] = a16(tb.p[e]) && a16(tb.g[e]) && a16(tb.m[e]) && a16(tb.v[e]) && ((uintptr_t)tb.q[e] & 7u) == 0;
+      blocks += (unsigned)nb;
+    }
+    if (tb.n == 0) {
+      if (t < num_tensors && counts[t] != 0)
+        return fail(E5MA_INVALID_VALUE, "e5b_adam_multi: tensor %d is too large for one launch; use e5ma_adam", t);
+      continue;
+    }
+    tb.first_block[tb.n] = blocks;
+    const cudaError_t err = pt == E5MA_BF16 ? adam_multi_g<E5MA_BF16>(gt, mt, qt, copy, a, tb, blocks, stream)
+                                            : adam_multi_g<E5MA_FP32>(gt, mt, qt, copy, a, tb, blocks, stream);
+    if (err != cudaSuccess) return cuda_fail(err, "e5b_adam_multi: kernel launch");
+  }
+  return E5MA_OK;
 }

@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <stdlib.h>
 #include "common.cuh"
+#include "../../include/e5m2effma_b200.h"
 
 namespace e5b {
 namespace tc {

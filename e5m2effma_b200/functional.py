@@ -240,9 +240,40 @@ def adam_step(param, grad, exp_avg, exp_avg_sq, *, lr, betas=(0.9, 0.999), eps=1
         _check(capi.adam(cfg, n, P, G, M, V, Q, torch.cuda.current_stream().cuda_stream), "e5ma_adam")
 
 
+def adam_step_multi(params, grads, exp_avgs, exp_avg_sqs, *, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, step,
+                    adamw=True, bias_correction=True, grad_scale=1.0):
+    """One Adam / AdamW step over lists of tensors that share a device and their dtypes, in as few kernel
+    launches as possible (e5b_adam_multi); same arithmetic as adam_step on each tensor."""
+    if not params:
+        return
+    dev = params[0].device
+    for lst, nm in ((params, "params"), (grads, "grads"), (exp_avgs, "exp_avgs"), (exp_avg_sqs, "exp_avg_sqs")):
+        if len(lst) != len(params):
+            raise ValueError(f"{nm} has {len(lst)} tensors, params has {len(params)}")
+        for t in lst:
+            if t.device != dev or not t.is_cuda:
+                raise ValueError(f"every tensor must be on {dev}")
+            if not t.is_contiguous():
+                raise ValueError(f"{nm} must be contiguous")
+    for p, g, m, v in zip(params, grads, exp_avgs, exp_avg_sqs):
+        if not (p.numel() == g.numel() == m.numel() == v.numel()):
+            raise ValueError("param, grad and moments of one entry must have the same number of elements")
+    if step < 1:
+        raise ValueError(f"step must be >= 1 (1-based), got {step}")
+    b1, b2 = betas
+    cfg = capi.AdamConfig(lr, b1, b2, eps, weight_decay, int(step), int(bool(adamw)), int(bool(bias_correction)), grad_scale)
+    T = lambda t: capi.tensor(t.data_ptr(), _dtype(t.dtype, "tensor"))
+    with torch.cuda.device(dev):
+        st = capi.adam_multi(cfg, [p.numel() for p in params], [T(p) for p in params], [T(g) for g in grads],
+                             [T(m) for m in exp_avgs], [T(v) for v in exp_avg_sqs], None,
+                             torch.cuda.current_stream().cuda_stream)
+    _check(st, "e5b_adam_multi")
+
+
 class AdamW(torch.optim.Optimizer):
-    """torch.optim-style AdamW (Adam with adamw=False) on the fused kernel, one launch per
-    parameter, as the reference's optimizer (binds/python/e5m2effma/optim.py:31-53)."""
+    """torch.optim-style AdamW (Adam with adamw=False) on the fused kernel; same hyper-parameters and
+    state as the reference's optimizer (binds/python/e5m2effma/optim.py:31-53), but parameters that share a
+    device, dtypes and step count are updated by shared launches (e5b_adam_multi) instead of one each."""
 
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, *, adamw=True,
                  state_dtype=None):
@@ -262,6 +293,7 @@ class AdamW(torch.optim.Optimizer):
             with torch.enable_grad():
                 loss = closure()
         for group in self.param_groups:
+            buckets = {}   # (device, param dtype, grad dtype, step) -> tensors that can share launches
             for p in group["params"]:
                 if p.grad is None:
                     continue
@@ -273,6 +305,11 @@ class AdamW(torch.optim.Optimizer):
                     st["exp_avg"] = torch.zeros_like(p, dtype=group["state_dtype"], memory_format=torch.contiguous_format)
                     st["exp_avg_sq"] = torch.zeros_like(p, dtype=group["state_dtype"], memory_format=torch.contiguous_format)
                 st["step"] += 1
-                adam_step(p, p.grad, st["exp_avg"], st["exp_avg_sq"], lr=group["lr"], betas=group["betas"],
-                          eps=group["eps"], weight_decay=group["weight_decay"], step=st["step"], adamw=group["adamw"])
+                if not (p.is_contiguous() and p.grad.is_contiguous()):
+                    raise ValueError("parameters and gradients must be contiguous")
+                b = buckets.setdefault((p.device, p.dtype, p.grad.dtype, st["step"]), ([], [], [], []))
+                b[0].append(p); b[1].append(p.grad); b[2].append(st["exp_avg"]); b[3].append(st["exp_avg_sq"])
+            for (_, _, _, stp), (ps, gs, ms, vs) in buckets.items():
+                adam_step_multi(ps, gs, ms, vs, lr=group["lr"], betas=group["betas"], eps=group["eps"],
+                                weight_decay=group["weight_decay"], step=stp, adamw=group["adamw"])
         return loss

@@ -119,3 +119,15 @@ def test_no_device_gives_an_error_not_a_fallback():
         pytest.skip("a GPU is present")
     st = gemm()
     assert st in (capi.CUDA_ERROR, capi.NOT_SUPPORTED) and capi.last_error()
+
+
+def test_adam_multi_rejects():
+    f32, bf = T(capi.FP32), T(capi.BF16)
+    cfg = adam_cfg()
+    assert capi.adam_multi(None, [8], [f32], [f32], [f32], [f32]) == capi.INVALID_VALUE
+    assert capi.adam_multi(adam_cfg(step=0), [8], [f32], [f32], [f32], [f32]) == capi.INVALID_VALUE
+    assert capi.adam_multi(cfg, [8], [T(capi.FP16)], [f32], [f32], [f32]) == capi.NOT_SUPPORTED
+    assert capi.adam_multi(cfg, [8, 8], [f32, bf], [f32, f32], [f32, f32], [f32, f32]) == capi.INVALID_VALUE
+    assert "differs in dtype" in capi.last_error()
+    assert capi.adam_multi(cfg, [8], [T(capi.FP32, data=None)], [f32], [f32], [f32]) == capi.INVALID_VALUE
+    assert capi.adam_multi(cfg, [], [], [], [], []) == capi.OK and capi.last_error() == ""

@@ -82,3 +82,46 @@ def test_adamw_multi_step_matches_torch_closely():
         opt.step()
         fx.adam_step(p, g, m, v, lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1, step=step)
     assert torch.allclose(p, p1.detach(), rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("pt,gt,mt,with_copy", [(BF16, BF16, BF16, True), (FP32, FP16, FP32, False), (FP32, BF16, BF16, True)])
+def test_adam_multi_equals_single_tensor_calls(pt, gt, mt, with_copy):
+    """e5b_adam_multi over 30 tensors of ragged sizes (more than one launch, tails, an empty tensor, an
+    unaligned one) gives the same bits as one e5ma_adam call per tensor."""
+    import torch
+    from e5m2effma_b200 import capi
+    rng = np.random.default_rng(99)
+    sizes = [0, 1, 7, 8, 100003, 16384, 16385, 40000] + [int(x) for x in rng.integers(1, 70000, 22)]
+    cfgd = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, step=3, adamw=1, bias_correction=1, grad_scale=0.5)
+    cfg = capi.AdamConfig(*[cfgd[f[0]] for f in capi.AdamConfig._fields_])
+    S = orc.NP_STORAGE
+    hold, A, B = [], [], []
+    for idx, n in enumerate(sizes):
+        p = fill(pt, max(n, 1), 1.0, rng); g = fill(gt, max(n, 1), 0.1, rng); m = fill(mt, max(n, 1), 0.01, rng)
+        v = orc.encode(mt, np.abs(orc.decode(mt, m)) * np.float32(0.01))
+        off = orc.esize(gt) if idx == 5 else 0       # one unaligned gradient
+        two = []
+        for _ in range(2):
+            bufs = [to_dev(p), to_dev(g, off), to_dev(m), to_dev(v), to_dev(np.full(max(n, 1), 0xA5, np.uint8)),
+                    to_dev(np.array([32.0], np.float32)), to_dev(np.zeros(1, np.float32))]
+            hold.append(bufs)
+            two.append(bufs)
+        A.append(two[0]); B.append(two[1])
+    def tensors(bufs):
+        P = [capi.tensor(b[0][1], pt) for b in bufs]; G = [capi.tensor(b[1][1], gt) for b in bufs]
+        M = [capi.tensor(b[2][1], mt) for b in bufs]; V = [capi.tensor(b[3][1], mt) for b in bufs]
+        Q = [capi.tensor(b[4][1], E4M3, None, b[5][1], b[6][1]) for b in bufs] if with_copy else None
+        return P, G, M, V, Q
+    P, G, M, V, Q = tensors(A)
+    st = capi.adam_multi(cfg, sizes, P, G, M, V, Q, torch.cuda.current_stream().cuda_stream)
+    assert st == capi.OK, capi.last_error()
+    P, G, M, V, Q = tensors(B)
+    for i, n in enumerate(sizes):
+        st = capi.adam(cfg, n, P[i], G[i], M[i], V[i], Q[i] if with_copy else None, torch.cuda.current_stream().cuda_stream)
+        assert st == capi.OK, capi.last_error()
+    torch.cuda.synchronize()
+    for i, n in enumerate(sizes):
+        for slot, dt in ((0, pt), (2, mt), (3, mt)):
+            assert np.array_equal(from_dev(A[i][slot][0], S[dt], n).view(np.uint8), from_dev(B[i][slot][0], S[dt], n).view(np.uint8)), (i, slot)
+        assert np.array_equal(from_dev(A[i][4][0], np.uint8, max(n, 1)), from_dev(B[i][4][0], np.uint8, max(n, 1))), (i, "fp8 copy")
+        assert from_dev(A[i][6][0], np.float32, 1)[0] == from_dev(B[i][6][0], np.float32, 1)[0], (i, "amax")
