@@ -107,6 +107,16 @@ __device__ __forceinline__ uint32_t enc_bf16(float v) { return enc_bf16x2(v, 0.f
 __device__ __forceinline__ uint32_t enc_f16(float v) { return __half_as_ushort(__float2half_rn(v)); }
 __device__ __forceinline__ uint32_t enc_f16x2(float lo, float hi) { return enc_f16(lo) | (enc_f16(hi) << 16); }
 
+// ---- 32-byte global accesses (sm_100: 256-bit vector loads / stores), streaming cache hints ------
+__device__ __forceinline__ void ld32B_stream(const void *p, uint32_t r[8]) {
+  asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "l"(p));
+}
+__device__ __forceinline__ void st32B_stream(void *p, const uint32_t r[8]) {
+  asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"l"(p), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+
 // ---- typed scalar access ---------------------------------------------------------------------
 __device__ __forceinline__ float ld_or_one(const float *p) { return p ? *p : 1.0f; }
 

@@ -59,9 +59,28 @@ e5ma_status require_blackwell(const char *who, DeviceProps *out) {
 
 // ---- cast kernel -----------------------------------------------------------------------------
 // 16 consecutive elements per step: 16-byte accesses for every dtype (FP32: four of them).
-template <int T>
+// WIDE: the array base is 32-byte aligned, so 2- and 4-byte dtypes use 32-byte accesses (half as many
+// memory instructions; the narrow-to-wide casts are limited by the load/store queues, not by arithmetic).
+template <int T, bool WIDE>
 __device__ __forceinline__ void load16(const void *base, size_t i, float sinv, float v[16]) {
-  if (T == E5MA_FP32) {
+  if (WIDE && T == E5MA_FP32) {
+    const uint8_t *p = reinterpret_cast<const uint8_t *>(base) + i * 4;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      uint32_t r[8];
+      ld32B_stream(p + 32 * q, r);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[8 * q + e] = __uint_as_float(r[e]);
+    }
+  } else if (WIDE && (T == E5MA_BF16 || T == E5MA_FP16)) {
+    uint32_t w[8];
+    ld32B_stream(reinterpret_cast<const uint8_t *>(base) + i * 2, w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      if (T == E5MA_BF16) { v[2 * e] = __uint_as_float(w[e] << 16); v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u); }
+      else { const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[e])); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+    }
+  } else if (T == E5MA_FP32) {
     const float4 *p = reinterpret_cast<const float4 *>(base) + i / 4;
 #pragma unroll
     for (int q = 0; q < 4; ++q) { const float4 a = __ldcs(p + q); v[4 * q] = a.x; v[4 * q + 1] = a.y; v[4 * q + 2] = a.z; v[4 * q + 3] = a.w; }
@@ -88,9 +107,23 @@ __device__ __forceinline__ void load16(const void *base, size_t i, float sinv, f
     }
   }
 }
-template <int T>
+template <int T, bool WIDE>
 __device__ __forceinline__ void store16(void *base, size_t i, float qs, const float v[16]) {
-  if (T == E5MA_FP32) {
+  if (WIDE && T == E5MA_FP32) {
+    uint8_t *p = reinterpret_cast<uint8_t *>(base) + i * 4;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      uint32_t r[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) r[e] = __float_as_uint(v[8 * q + e]);
+      st32B_stream(p + 32 * q, r);
+    }
+  } else if (WIDE && (T == E5MA_BF16 || T == E5MA_FP16)) {
+    uint32_t w[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) w[e] = T == E5MA_BF16 ? enc_bf16x2(v[2 * e], v[2 * e + 1]) : enc_f16x2(v[2 * e], v[2 * e + 1]);
+    st32B_stream(reinterpret_cast<uint8_t *>(base) + i * 2, w);
+  } else if (T == E5MA_FP32) {
     float4 *p = reinterpret_cast<float4 *>(base) + i / 4;
 #pragma unroll
     for (int q = 0; q < 4; ++q) __stcs(p + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
@@ -114,14 +147,16 @@ __device__ __forceinline__ void store16(void *base, size_t i, float qs, const fl
   }
 }
 
-// VEC: both pointers are 16-byte aligned.  Whole 16-element groups go through the vector path in a
-// grid-stride loop; the remaining count % 16 elements (or everything when !VEC) go one at a time.
-template <int TS, int TD, bool VEC>
+// MODE 0: element by element.  MODE 1: both pointers are 16-byte aligned: whole 16-element groups go
+// through the vector path in a grid-stride loop, the remaining count % 16 elements one at a time.
+// MODE 2: both pointers are 32-byte aligned: as MODE 1 with 32-byte accesses.
+template <int TS, int TD, int MODE>
 __global__ void __launch_bounds__(256) cast_kernel(const void *__restrict__ src, void *__restrict__ dst, size_t count,
                                                    const float *sinv_p, const float *scale_p, float *amax) {
   const float sinv = ld_or_one(sinv_p), qs = ld_or_one(scale_p);
   float mx = 0.f;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (size_t)gridDim.x * blockDim.x;
+  constexpr bool VEC = MODE != 0, WIDE = MODE == 2;
   const size_t groups = VEC ? count / 16 : 0;
   // G groups per step so that every thread keeps 64 bytes of loads in flight whatever the source width
   constexpr int G = 4 / elem_bytes(TS);
@@ -129,20 +164,20 @@ __global__ void __launch_bounds__(256) cast_kernel(const void *__restrict__ src,
   for (; gidx + (G - 1) * nthr < groups; gidx += G * nthr) {
     float v[G][16];
 #pragma unroll
-    for (int u = 0; u < G; ++u) load16<TS>(src, (gidx + u * nthr) * 16, sinv, v[u]);
+    for (int u = 0; u < G; ++u) load16<TS, WIDE>(src, (gidx + u * nthr) * 16, sinv, v[u]);
 #pragma unroll
     for (int u = 0; u < G; ++u) {
 #pragma unroll
       for (int e = 0; e < 16; ++e) mx = fmaxf(mx, fabsf(v[u][e]));
-      store16<TD>(dst, (gidx + u * nthr) * 16, qs, v[u]);
+      store16<TD, WIDE>(dst, (gidx + u * nthr) * 16, qs, v[u]);
     }
   }
   for (; gidx < groups; gidx += nthr) {
     float v[16];
-    load16<TS>(src, gidx * 16, sinv, v);
+    load16<TS, WIDE>(src, gidx * 16, sinv, v);
 #pragma unroll
     for (int e = 0; e < 16; ++e) mx = fmaxf(mx, fabsf(v[e]));
-    store16<TD>(dst, gidx * 16, qs, v);
+    store16<TD, WIDE>(dst, gidx * 16, qs, v);
   }
   for (size_t i = groups * 16 + tid; i < count; i += nthr) {
     const float v = load_elem(TS, src, i, sinv);
@@ -161,8 +196,10 @@ static cudaError_t cast_launch(const void *src, void *dst, size_t count, const f
   const size_t cap = (size_t)sms * 16;   // two sweeps of full occupancy, then grid-stride
   if (blocks > cap) blocks = cap;
   if (blocks == 0) blocks = 1;
-  if (vec) cast_kernel<TS, TD, true><<<(unsigned)blocks, 256, 0, s>>>(src, dst, count, sinv, scale, amax);
-  else cast_kernel<TS, TD, false><<<(unsigned)blocks, 256, 0, s>>>(src, dst, count, sinv, scale, amax);
+  const bool wide = (((uintptr_t)src | (uintptr_t)dst) & 31u) == 0;
+  if (wide) cast_kernel<TS, TD, 2><<<(unsigned)blocks, 256, 0, s>>>(src, dst, count, sinv, scale, amax);
+  else if (vec) cast_kernel<TS, TD, 1><<<(unsigned)blocks, 256, 0, s>>>(src, dst, count, sinv, scale, amax);
+  else cast_kernel<TS, TD, 0><<<(unsigned)blocks, 256, 0, s>>>(src, dst, count, sinv, scale, amax);
   return cudaGetLastError();
 }
 

@@ -126,7 +126,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
         int i0, j0, rows;
         item_at(t, i0, j0, rows);
         const bool half_tile = rows != BI;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        // successive tiles of a CTA walk K in opposite directions: the next tile starts with the k-blocks that
+        // were read last and are still in L2 (the sum does not care about the order of its k-blocks)
+        const bool backwards = ((t / (int)gridDim.x) & 1) != 0;
+        for (int kq = 0; kq < kblocks; ++kq, ++it) {
+          const int kb = backwards ? kblocks - 1 - kq : kq;
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)kb)) { ok = false; break; }

@@ -153,7 +153,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
         j0 += (int)rank * 128;            // and its 128 rows of the M side
         const CUtensorMap *mi = cols == P_TILE ? &map_i : (cols == P_TILE / 2 ? &map_i2 : &map_i4);
         const uint32_t pair_bytes = 2u * (P_HALF_BYTES + (uint32_t)(cols / 2) * STAGE_K_BYTES);
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        // Successive tiles of a pair walk K in opposite directions: the next tile starts with the k-blocks its
+        // predecessors in the same band read last, which are the ones still in L2 (the sum does not care
+        // about the order of its k-blocks).
+        const bool backwards = ((t / pairs) & 1) != 0;
+        for (int kq = 0; kq < kblocks; ++kq, ++it) {
+          const int kb = backwards ? kblocks - 1 - kq : kq;
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)kb)) { ok = false; break; }
