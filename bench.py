@@ -212,6 +212,9 @@ def run_reference(args, metric, unit, config):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--amax-reduce", default="inline", choices=["overlap", "inline", "off"],
+                    help="N > 1: the per-step max-all-reduce of amax runs beside the next step, inline after each step, "
+                         "or not at all (experiments)")
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c2")
@@ -285,12 +288,31 @@ def main():
         else:
             w.launch(sptr)
 
+    # N > 1: the amax of a step is max-reduced over the ranks (one float), by default inline after the step.
+    # "overlap" lets the reduction of step i run beside step i + 1 (two amax slots alternate, a slot is reused only
+    # after its reduction has completed, all reductions complete inside the timed region); measured slower at N = 2
+    # (0.39-0.43 ms against 0.355 ms per step): the persistent GEMM sizes its grid to every SM, and a reduction
+    # kernel that holds an SM when the next GEMM starts delays one of its CTA pairs by a whole round.
     amax_t = getattr(w, "amax", None)
+    reduce_amax = world > 1 and amax_t is not None and args.amax_reduce != "off"
+    overlap = args.amax_reduce == "overlap"
+    amax_slots = [amax_t, amax_t.clone()] if reduce_amax else None
+    pending = []
 
     def step(i):
+        if reduce_amax and overlap:
+            if len(pending) == 2:
+                pending.pop(0).wait()
+            w.amax = amax_slots[i % 2]
         one_pass(i)
-        if world > 1 and amax_t is not None:
-            dist.all_reduce(amax_t, op=dist.ReduceOp.MAX)
+        if reduce_amax and overlap:
+            pending.append(dist.all_reduce(w.amax, op=dist.ReduceOp.MAX, async_op=True))
+        elif reduce_amax:
+            dist.all_reduce(w.amax, op=dist.ReduceOp.MAX)
+
+    def drain():
+        while pending:
+            pending.pop(0).wait()
 
     def barrier():
         if world > 1:
@@ -302,6 +324,7 @@ def main():
     # kernels (the 4096^3 GEMM, the GEMV) are not timed behind the Python / ctypes launch path.
     for i in range(args.warmup):
         step(i)
+    drain()
     barrier()
     graph = None
     if not args.no_graph:
@@ -313,6 +336,7 @@ def main():
             with torch.cuda.graph(graph, stream=cs):
                 for i in range(args.steps):
                     step(i)
+                drain()
             sptr = sptr_saved
         graph.replay()          # one untimed replay (also warms the instantiated graph)
         barrier()
@@ -325,9 +349,13 @@ def main():
     else:
         for i in range(args.steps):
             step(i)
+        drain()
     e1.record(stream)
     barrier()
     ms = e0.elapsed_time(e1)
+    if reduce_amax:
+        torch.maximum(amax_slots[0], amax_slots[1], out=amax_slots[0])
+        w.amax = amax_t
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -143,12 +143,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
           // K-major operand: one box of all its rows.  MN-major operand: one box per 128 bytes of rows (each
           // box is a full stage of k-rows x 128 bytes), the boxes lie MN_BOX_BYTES apart.
           constexpr int EB = KIND == 0 ? 1 : 2, MN_BOX_BYTES = (STAGE_K_BYTES / EB) * 128;
-          if (CONV == 0 && md.mn_m) {
+          if (CONV == 2 && md.mn_m) {
+            tma_load_2d(sraw, &map_j, j0, kc, full_bar(s));     // 64 k-rows x 128 raw FP8 codes along j
+          } else if (md.mn_m) {
             for (int b = 0; b < BM * EB / 128; ++b) tma_load_2d(sj + b * MN_BOX_BYTES, &map_j, j0 + b * (128 / EB), kc, full_bar(s));
           } else {
             tma_load_2d(CONV == 2 ? sraw : sj, &map_j, kc, j0, full_bar(s));
           }
-          if (CONV == 0 && md.mn_n) {
+          if (CONV != 1 && md.mn_n) {
             for (int b = 0; b < rows * EB / 128; ++b) tma_load_2d(si + b * MN_BOX_BYTES, &map_i, i0 + b * (128 / EB), kc, full_bar(s));
           } else {
             tma_load_2d(CONV == 1 ? sraw : si, half_tile ? &map_ih : &map_i, kc, i0, full_bar(s));
@@ -180,7 +182,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
           // MN-major: one MMA spans 32 bytes of K = 32 (FP8) or 16 (BF16) k-rows of 128 bytes = +256 / +128.
           constexpr int EB = KIND == 0 ? 1 : 2;
           constexpr uint32_t MN_BOX_BYTES = (STAGE_K_BYTES / EB) * 128, MN_STEP = (MMA_K_BYTES / EB) * 128 / 16;
-          const bool mnj = CONV == 0 && md.mn_m, mni = CONV == 0 && md.mn_n;
+          const bool mnj = CONV != 1 && md.mn_m, mni = CONV != 1 && md.mn_n;
           const uint64_t dj = mnj ? mnmajor_sw128_desc(sj, MN_BOX_BYTES) : kmajor_sw128_desc(sj);
           const uint64_t di = mni ? mnmajor_sw128_desc(si, MN_BOX_BYTES) : kmajor_sw128_desc(si);
           const uint32_t stepj = mnj ? MN_STEP : 2u, stepi = mni ? MN_STEP : 2u;
@@ -221,14 +223,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
           uint8_t *dst = stage + (CONV == 1 ? C::J_BYTES : 0);
 #pragma unroll
           for (int idx = ct; idx < C::RAW_ROWS * 4; idx += 32 * EPI_WARPS) {
-            const int r = idx >> 2, c = idx & 3;
             const uint4 q = *reinterpret_cast<const uint4 *>(raw + idx * 16);
             uint32_t w[8];
             fp8x4_to_bf16x2<FT>(q.x, w[0], w[1]);
             fp8x4_to_bf16x2<FT>(q.y, w[2], w[3]);
             fp8x4_to_bf16x2<FT>(q.z, w[4], w[5]);
             fp8x4_to_bf16x2<FT>(q.w, w[6], w[7]);
-            uint8_t *row = dst + r * 128;
+            // K-contiguous operand: raw row r = 64 codes along k, four chunks c.  Operand contiguous along j (CONV 2
+            // only): raw row r = k-row of 128 codes along j, eight chunks; chunks 0..3 belong to the first 64-column
+            // box of the MN-major BF16 layout, 4..7 to the second.  Either way a raw chunk becomes the BF16 chunks
+            // 2c, 2c+1 of a 128-byte row, swizzled with the row index.
+            const bool mn = CONV == 2 && md.mn_m;
+            const int r = mn ? idx >> 3 : idx >> 2, c = idx & 3;
+            uint8_t *row = dst + r * 128 + (mn ? ((idx >> 2) & 1) * (64 * 128) : 0);
             *reinterpret_cast<uint4 *>(row + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             *reinterpret_cast<uint4 *>(row + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
           }
@@ -348,9 +355,8 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   if (a_dtype == E5MA_FP32 || b_dtype == E5MA_FP32) return cudaErrorNotSupported;
   const bool f8 = is_fp8(a_dtype) && is_fp8(b_dtype);
   const int conv = f8 ? 0 : (is_fp8(a_dtype) ? 1 : (is_fp8(b_dtype) ? 2 : 0));
-  // operands stored contiguous along m / n (transa = N, transb = T) are read as MN-major MMA operands; the
-  // mixed pairs (which rewrite an operand in shared memory) and the CTA-pair kernel take K-contiguous ones only
-  if ((!a_kc || !b_kc) && conv != 0) return cudaErrorNotSupported;
+  // operands stored contiguous along m / n (transa = N, transb = T) are read as MN-major MMA operands (the
+  // widened FP8 operand of a mixed pair is written in that layout too); the CTA-pair kernel takes K-contiguous ones only
   const int kind = f8 ? 0 : 1;
   const int ft = conv == 1 ? a_dtype : (conv == 2 ? b_dtype : E5MA_E5M2);
   // CTA pairs (gemm_tc2.cuh) for big unmixed problems: 256 x 256 tiles, half the operand bytes per CTA
@@ -394,7 +400,7 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   CUtensorMap mi, mj, mih;   // mih: the N-side operand with half-height boxes, for the half tiles of the last round
   const bool n_kc = tr ? b_kc : a_kc, m_kc = tr ? a_kc : b_kc;   // storage of the N-side / M-side operand
   if (!(n_kc ? make_map(&mi, pn, elem_bytes(dn), k, en, ldn, bi, false) : make_map_mn(&mi, pn, elem_bytes(dn), k, en, ldn)) ||
-      !(m_kc ? make_map(&mj, pm, elem_bytes(dm), k, em, ldm, BM, conv != 0) : make_map_mn(&mj, pm, elem_bytes(dm), k, em, ldm)) ||
+      !(m_kc ? make_map(&mj, pm, elem_bytes(dm), k, em, ldm, BM, conv != 0) : make_map_mn(&mj, pm, elem_bytes(dm), k, em, ldm, conv != 0)) ||
       !(n_kc ? make_map(&mih, pn, elem_bytes(dn), k, en, ldn, bi / 2, false) : make_map_mn(&mih, pn, elem_bytes(dn), k, en, ldn)))
     return cudaErrorNotSupported;
   // operand formats of the instruction: FP8 codes for kind::f8f6f4 (E4M3 = 0, E5M2 = 1), BF16 = 1 for kind::f16

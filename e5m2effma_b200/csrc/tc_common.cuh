@@ -331,17 +331,18 @@ inline EncodeTiledFn encode_fn() {
 // in shared memory first (raw) gets plain 64-byte rows.
 // MN-contiguous operand (rows x k elements stored k x rows... i.e. element (r, kk) at r + kk * ld): boxes of
 // 128 bytes of rows x one stage of k (128 FP8 / 64 BF16 k-rows), 128-byte swizzle.
-inline bool make_map_mn(CUtensorMap *map, const void *base, int elem_bytes, int k, int rows, int ld) {
+inline bool make_map_mn(CUtensorMap *map, const void *base, int elem_bytes, int k, int rows, int ld, bool raw = false) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)rows, (cuuint64_t)k};
   const cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
-  const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)(STAGE_K_BYTES / elem_bytes)};
+  // raw (an FP8 operand that will be widened to BF16): 64 k-rows of 128 codes, not swizzled
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)(raw ? STAGE_K_BYTES / 2 : STAGE_K_BYTES / elem_bytes)};
   const cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   return fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
-         CUDA_SUCCESS;
+            raw ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 inline bool make_map(CUtensorMap *map, const void *base, int elem_bytes, int k, int rows, int ld, int box_rows, bool raw) {
