@@ -26,10 +26,14 @@
 //     instruction descriptor and the element type of the tensor maps.
 //   * FP8 x BF16 pairs (either order) also run kind::f16: products must stay exact, so the FP8
 //     operand is widened to BF16, which is exact (at most 4 significant bits).  TMA brings its raw
-//     bytes (64 per row and k-block) into the stage; the eight epilogue warps rewrite them as BF16 in
-//     the swizzled K-major layout, fence towards the async proxy and signal the MMA warp, k-block by
+//     bytes (8 KiB per k-block of 64) into the stage; the eight epilogue warps rewrite them as BF16 in
+//     the swizzled layout that matches the operand's storage (K-major, or MN-major when it is stored
+//     contiguous along m / n), fence towards the async proxy and signal the MMA warp, k-block by
 //     k-block, and only then drain the tile's accumulator (mixed pairs have long K: the epilogue is
-//     short next to the mainloop, and the TMA ring keeps filling meanwhile).
+//     short next to the mainloop, and the TMA ring keeps filling meanwhile).  Measured alternatives
+//     that were slower on this part: widening into tensor memory with the MMA reading its A operand
+//     from there (each such MMA took ~280 clocks whatever its N), separate rings for raw and widened
+//     data, CTA pairs (the extra cross-CTA signalling lengthens the per-stage chain).
 //   * No cluster features are used: every CTA loads its own operand boxes.
 //
 // Every wait on an mbarrier is bounded.  A wait that runs out records a fault word, raises a
@@ -89,7 +93,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
   // idesc_half) so that the round takes half as long.  Every role derives the same list from this.
   const int grid_n = gridDim.x;
   const int full_items = (tiles / grid_n) * grid_n, rem = tiles - full_items;
-  const bool split = CONV == 0 && md.split && rem > 0 && 2 * rem <= grid_n;
+  const bool split = md.split && rem > 0 && 2 * rem <= grid_n;
   const int items = split ? full_items + 2 * rem : tiles;
   const auto item_at = [&](int item, int &i0, int &j0, int &rows) {
     int tile = item, hf = 0;
@@ -207,10 +211,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
       int i0, j0, rows;
       item_at(t, i0, j0, rows);
       if (CONV != 0) {
-        // Mixed pairs: these warps first widen the FP8 operand of every k-block of the tile (raw FP8 rows ->
-        // BF16 rows in the swizzled K-major layout), then drain the accumulator.  A raw row is 64 bytes = four
-        // 16-byte chunks; chunk c of row r (k = 16c .. 16c+15) becomes the two 16-byte chunks 2c, 2c+1 of the
-        // 128-byte BF16 row, which the 128-byte swizzle keeps at chunk positions (2c) ^ (r & 7), (2c+1) ^ (r & 7).
+        // Mixed pairs: these warps first widen the FP8 operand of every k-block of the tile (widen_block), then
+        // drain the accumulator.
         const int ct = threadIdx.x - 64;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % C::STAGES;
@@ -221,24 +223,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
           uint8_t *stage = smem_raw + (ring - smem_u32(smem_raw)) + s * C::STAGE_BYTES;
           const uint8_t *raw = stage + C::J_BYTES + C::I_BYTES;
           uint8_t *dst = stage + (CONV == 1 ? C::J_BYTES : 0);
-#pragma unroll
-          for (int idx = ct; idx < C::RAW_ROWS * 4; idx += 32 * EPI_WARPS) {
-            const uint4 q = *reinterpret_cast<const uint4 *>(raw + idx * 16);
-            uint32_t w[8];
-            fp8x4_to_bf16x2<FT>(q.x, w[0], w[1]);
-            fp8x4_to_bf16x2<FT>(q.y, w[2], w[3]);
-            fp8x4_to_bf16x2<FT>(q.z, w[4], w[5]);
-            fp8x4_to_bf16x2<FT>(q.w, w[6], w[7]);
-            // K-contiguous operand: raw row r = 64 codes along k, four chunks c.  Operand contiguous along j (CONV 2
-            // only): raw row r = k-row of 128 codes along j, eight chunks; chunks 0..3 belong to the first 64-column
-            // box of the MN-major BF16 layout, 4..7 to the second.  Either way a raw chunk becomes the BF16 chunks
-            // 2c, 2c+1 of a 128-byte row, swizzled with the row index.
-            const bool mn = CONV == 2 && md.mn_m;
-            const int r = mn ? idx >> 3 : idx >> 2, c = idx & 3;
-            uint8_t *row = dst + r * 128 + (mn ? ((idx >> 2) & 1) * (64 * 128) : 0);
-            *reinterpret_cast<uint4 *>(row + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-            *reinterpret_cast<uint4 *>(row + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-          }
+          if (CONV == 2 && md.mn_m) widen_block<FT, true>(raw, dst, ct);
+          else widen_block<FT, false>(raw, dst, ct);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
           __syncwarp();
           if (lane == 0) mbar_arrive(ready_bar(s));

@@ -309,6 +309,29 @@ __device__ __forceinline__ float drain32_t(const OutDesc &o, const OutScalars &r
   return mx;
 }
 
+// Widening of the FP8 operand of a mixed pair, one k-block: 512 raw 16-byte chunks -> 1024 BF16 chunks in the
+// 128-byte-swizzled layout.  ct: index of the thread among the 256 epilogue threads.  K-contiguous operand
+// (MN = false): raw row r = 64 codes along k of row r, four chunks c.  Operand contiguous along its rows' index
+// (MN = true): raw row r = k-row of 128 codes, eight chunks; chunks 0..3 belong to the first 64-row box of the
+// MN-major BF16 layout, 4..7 to the second.  Either way raw chunk c becomes the BF16 chunks 2c, 2c+1 of a
+// 128-byte row, swizzled with the row index.
+template <int FT, bool MN>
+__device__ __forceinline__ void widen_block(const uint8_t *raw, uint8_t *dst, int ct) {
+#pragma unroll
+  for (int idx = ct; idx < 512; idx += 32 * EPI_WARPS) {
+    const uint4 q = *reinterpret_cast<const uint4 *>(raw + idx * 16);
+    uint32_t w[8];
+    fp8x4_to_bf16x2<FT>(q.x, w[0], w[1]);
+    fp8x4_to_bf16x2<FT>(q.y, w[2], w[3]);
+    fp8x4_to_bf16x2<FT>(q.z, w[4], w[5]);
+    fp8x4_to_bf16x2<FT>(q.w, w[6], w[7]);
+    const int r = MN ? idx >> 3 : idx >> 2, c = idx & 3;
+    uint8_t *row = dst + r * 128 + (MN ? ((idx >> 2) & 1) * (64 * 128) : 0);
+    *reinterpret_cast<uint4 *>(row + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4 *>(row + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -345,6 +368,7 @@ inline bool make_map_mn(CUtensorMap *map, const void *base, int elem_bytes, int 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// raw: boxes of 64 FP8 codes per row, not swizzled (an operand that will be widened to BF16)
 inline bool make_map(CUtensorMap *map, const void *base, int elem_bytes, int k, int rows, int ld, int box_rows, bool raw) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;

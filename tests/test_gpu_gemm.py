@@ -102,6 +102,28 @@ def test_mixed_pairs_all_layouts_within_tolerance(case):
     assert capi.gemm_fault() == 0
 
 
+def mixed_large_cases():
+    """FP8 x BF16 problems with more tiles than SMs (several rounds per CTA, so every ring of the kernel wraps
+    across tile boundaries): FP8 on either side, ragged last tiles, a partly filled last round (half tiles), k tails."""
+    cases = []
+    for idx, (m, n, k) in enumerate([(2304, 2200, 336), (2100, 2560, 208), (4096, 2304, 144)]):
+        for at, bt in [(E5M2, BF16), (BF16, E4M3)]:
+            vec = (1 if at != BF16 else 2) if idx != 1 else 0
+            dt = [FP32, BF16, E5M2][idx]
+            cases.append(GemmCase(1, 0, m, n, k, at, bt, dt, -1, BF16 if idx != 2 else -1, 1.0 if idx else 0.75,
+                                  1.0 if dt == FP32 else 0.0, vec=vec, seed=300 + 2 * idx + (at == BF16)))
+    return cases
+
+
+@pytest.mark.parametrize("case", mixed_large_cases(), ids=lambda c: c.label())
+def test_mixed_pairs_many_tiles_within_tolerance(case):
+    from e5m2effma_b200 import capi
+    d = GemmData(case)
+    got, amax = d.run_gpu()
+    check_tolerance(d, got, amax)
+    assert capi.gemm_fault() == 0
+
+
 def test_runs_are_deterministic():
     d = GemmData(GemmCase(1, 0, 300, 200, 512, E5M2, E4M3, BF16, BF16, BF16, 1.0, 0.0, seed=77))
     a, am_a = d.run_gpu()
