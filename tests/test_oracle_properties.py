@@ -86,3 +86,24 @@ def test_nan_conventions_of_the_16_bit_encoders():
     nan = np.array([np.nan, -np.nan], np.float32)
     assert [int(t) for t in orc.encode(orc.BF16, nan)] == [0x7FC0, 0x7FC0]
     assert [int(t) for t in orc.encode(orc.FP16, nan)] == [0x7FFF, 0x7FFF]
+
+
+@pytest.mark.parametrize("adamw", [1, 0])
+def test_adam_follows_the_textbook_update(adamw):
+    """Three FP32 steps of the oracle against torch.optim.AdamW / Adam on the CPU.  The two order their FP32
+    operations differently, so agreement is to a few ulp, not bit for bit: this guards the formula (bias
+    corrections, decoupled against L2 weight decay, eps outside the square root), not the rounding."""
+    rng = np.random.default_rng(21)
+    n = 4096
+    p0 = (rng.standard_normal(n) * 0.05).astype(np.float32)
+    hp = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1)
+    p, m, v = p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    tp = torch.nn.Parameter(torch.from_numpy(p0.copy()))
+    cls = torch.optim.AdamW if adamw else torch.optim.Adam
+    opt = cls([tp], lr=hp["lr"], betas=(hp["beta1"], hp["beta2"]), eps=hp["eps"], weight_decay=hp["weight_decay"])
+    for step in (1, 2, 3):
+        g = (rng.standard_normal(n) * 1e-2).astype(np.float32)
+        orc.adam(dict(hp, step=step, adamw=adamw, bias_correction=1, grad_scale=1.0), p, orc.FP32, g, orc.FP32, m, v, orc.FP32)
+        tp.grad = torch.from_numpy(g.copy())
+        opt.step()
+    np.testing.assert_allclose(p, tp.detach().numpy(), rtol=2e-5, atol=1e-8)
