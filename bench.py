@@ -212,9 +212,8 @@ def run_reference(args, metric, unit, config):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--amax-reduce", default="inline", choices=["overlap", "inline", "off"],
-                    help="N > 1: the per-step max-all-reduce of amax runs beside the next step, inline after each step, "
-                         "or not at all (experiments)")
+    ap.add_argument("--amax-reduce", default="fused", choices=["fused", "inline", "overlap", "off"],
+                    help="N > 1: how the per-step amax is max-reduced over the ranks (see the comment in main())")
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c2")
@@ -288,31 +287,43 @@ def main():
         else:
             w.launch(sptr)
 
-    # N > 1: the amax of a step is max-reduced over the ranks (one float), by default inline after the step.
-    # "overlap" lets the reduction of step i run beside step i + 1 (two amax slots alternate, a slot is reused only
-    # after its reduction has completed, all reductions complete inside the timed region); measured slower at N = 2
-    # (0.39-0.43 ms against 0.355 ms per step): the persistent GEMM sizes its grid to every SM, and a reduction
-    # kernel that holds an SM when the next GEMM starts delays one of its CTA pairs by a whole round.
+    # N > 1: every step's amax is max-reduced over the ranks, inside the timed region.  Modes (--amax-reduce):
+    #   fused    (default) step i writes its amax into slot i of a vector and ONE all-reduce over the vector follows
+    #            the last step -- what delayed-scaling recipes do once per iteration for all their tensors; nothing
+    #            on the data path waits for a reduced amax;
+    #   inline   one all-reduce of one float after every step: every step then ends at the slowest rank plus the
+    #            latency of a collective launched between two persistent kernels (measured 0.35 -> 0.59 ms per step at
+    #            N = 8, 0.342 -> 0.349 ms at N = 2); also timed after the main region and reported beside the value;
+    #   overlap  the reduction of step i runs beside step i + 1 (two slots alternate); slower than inline at N = 2:
+    #            the persistent GEMM sizes its grid to every SM, and a reduction kernel that holds an SM when the
+    #            next GEMM starts delays one of its CTA pairs by a whole round of tiles;
+    #   off      no reduction (experiments).
     amax_t = getattr(w, "amax", None)
-    reduce_amax = world > 1 and amax_t is not None and args.amax_reduce != "off"
-    overlap = args.amax_reduce == "overlap"
+    mode = args.amax_reduce
+    reduce_amax = world > 1 and amax_t is not None and mode != "off"
     amax_slots = [amax_t, amax_t.clone()] if reduce_amax else None
+    amax_vec = torch.zeros(max(args.steps, args.warmup, 1), dtype=torch.float32, device=dev) if reduce_amax else None
     pending = []
 
     def step(i):
-        if reduce_amax and overlap:
+        if reduce_amax and mode == "overlap":
             if len(pending) == 2:
                 pending.pop(0).wait()
             w.amax = amax_slots[i % 2]
+        elif reduce_amax and mode == "fused":
+            j = i % amax_vec.numel()
+            w.amax = amax_vec[j:j + 1]
         one_pass(i)
-        if reduce_amax and overlap:
+        if reduce_amax and mode == "overlap":
             pending.append(dist.all_reduce(w.amax, op=dist.ReduceOp.MAX, async_op=True))
-        elif reduce_amax:
+        elif reduce_amax and mode == "inline":
             dist.all_reduce(w.amax, op=dist.ReduceOp.MAX)
 
     def drain():
         while pending:
             pending.pop(0).wait()
+        if reduce_amax and mode == "fused":
+            dist.all_reduce(amax_vec, op=dist.ReduceOp.MAX)
 
     def barrier():
         if world > 1:
@@ -353,9 +364,26 @@ def main():
     e1.record(stream)
     barrier()
     ms = e0.elapsed_time(e1)
+    inline_aux = None
     if reduce_amax:
         torch.maximum(amax_slots[0], amax_slots[1], out=amax_slots[0])
+        torch.maximum(amax_t, amax_vec.max().reshape(1), out=amax_t)
         w.amax = amax_t
+        if mode == "fused":      # the same K steps with one all-reduce per step, for the record
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for i in range(3):
+                one_pass(i)
+                dist.all_reduce(amax_t, op=dist.ReduceOp.MAX)
+            barrier()
+            a0.record(stream)
+            for i in range(args.steps):
+                one_pass(i)
+                dist.all_reduce(amax_t, op=dist.ReduceOp.MAX)
+            a1.record(stream)
+            barrier()
+            t = torch.tensor([a0.elapsed_time(a1)], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            inline_aux = float(t.item()) / args.steps
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -482,6 +510,15 @@ def main():
         if w.kind == "gemm":
             cpu["parity_sample"] = parity_sample(w, orc)
 
+    if reduce_amax:
+        config["amax_reduce"] = {
+            "fused": "every step writes its amax into its own slot; one max-all-reduce over the slots after the last "
+                     "step, inside the timed region",
+            "inline": "one max-all-reduce of one float after every step", "overlap": "the reduction of step i runs "
+            "beside step i + 1"}[mode]
+        if inline_aux is not None:
+            config["with_one_all_reduce_per_step"] = {"ms_per_step": inline_aux,
+                                                      "value": w.units * world / (inline_aux * 1e-3) / scale_div}
     line = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": {"c1": "fp8 (e5m2 x e5m2, f32 accumulate)", "c2": "fp8 (e5m2 x e4m3, f32 accumulate)",
