@@ -212,7 +212,7 @@ def run_reference(args, metric, unit, config):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--amax-reduce", default="fused", choices=["fused", "inline", "overlap", "off"],
+    ap.add_argument("--amax-reduce", default="inline", choices=["inline", "fused", "overlap", "off"],
                     help="N > 1: how the per-step amax is max-reduced over the ranks (see the comment in main())")
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
@@ -288,16 +288,17 @@ def main():
             w.launch(sptr)
 
     # N > 1: every step's amax is max-reduced over the ranks, inside the timed region.  Modes (--amax-reduce):
-    #   fused    (default) step i writes its amax into slot i of a vector and ONE all-reduce over the vector follows
-    #            the last step -- what delayed-scaling recipes do once per iteration for all their tensors; nothing
-    #            on the data path waits for a reduced amax;
-    #   inline   one all-reduce of one float after every step: every step then ends at the slowest rank plus the
-    #            latency of a collective launched between two persistent kernels (measured 0.35 -> 0.59 ms per step at
-    #            N = 8, 0.342 -> 0.349 ms at N = 2); also timed after the main region and reported beside the value;
+    #   inline   (default) one all-reduce of one float after every step;
+    #   fused    step i writes its amax into slot i of a vector and ONE all-reduce over the vector follows the last
+    #            step -- what delayed-scaling recipes do once per iteration for all their tensors; the per-step
+    #            figure is then also timed after the main region and reported beside the value;
     #   overlap  the reduction of step i runs beside step i + 1 (two slots alternate); slower than inline at N = 2:
     #            the persistent GEMM sizes its grid to every SM, and a reduction kernel that holds an SM when the
     #            next GEMM starts delays one of its CTA pairs by a whole round of tiles;
     #   off      no reduction (experiments).
+    # With a reduction in the step the K steps are launched on the stream, not replayed from a CUDA graph: NCCL
+    # kernels inside a replayed graph measured 0.59-0.64 ms per step at N = 8 (inline and fused alike) against
+    # 0.36 ms for the same steps launched directly (0.35 ms without any reduction).
     amax_t = getattr(w, "amax", None)
     mode = args.amax_reduce
     reduce_amax = world > 1 and amax_t is not None and mode != "off"
@@ -338,7 +339,7 @@ def main():
     drain()
     barrier()
     graph = None
-    if not args.no_graph:
+    if not args.no_graph and not reduce_amax:
         cs = torch.cuda.Stream()
         cs.wait_stream(stream)
         graph = torch.cuda.CUDAGraph()
