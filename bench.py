@@ -77,7 +77,7 @@ class ClockSampler(threading.Thread):
         except Exception:
             self.nv = None
 
-    def run(self):
+    def sample(self):
         if self.nv is None:
             return
         nv = self.nv
@@ -85,16 +85,29 @@ class ClockSampler(threading.Thread):
                  nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
                  nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
                  nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap"}
+        try:
+            self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+            r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            for bit, nm in names.items():
+                if r & bit:
+                    self.reasons.add(nm)
+        except Exception:
+            pass
+
+    def run(self):
         while not self.stop_flag:
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
-                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
-                for bit, nm in names.items():
-                    if r & bit:
-                        self.reasons.add(nm)
-            except Exception:
-                pass
+            self.sample()
             time.sleep(0.005)
+
+    def poll_until(self, event):
+        """Samples from the calling thread while the GPU works through what has already been enqueued, until
+        `event` has completed.  Used for the device-resident region: a sampling thread beside the thread that
+        launches delays launches now and then, and with a collective in every step all ranks pay for each
+        such delay (measured at N = 8: 0.59-0.70 ms per step with the thread, 0.36 ms without)."""
+        self.sample()
+        while not event.query():
+            self.sample()
+            time.sleep(0.0005)
 
     def summary(self):
         s = sorted(self.samples)
@@ -212,6 +225,9 @@ def run_reference(args, metric, unit, config):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--settle-s", type=float, default=0.0,
+                    help="N > 1 with a collective in the step: seconds of untimed steps after the warm-up, until the "
+                         "power-capped clocks have settled")
     ap.add_argument("--amax-reduce", default="inline", choices=["inline", "fused", "overlap", "off"],
                     help="N > 1: how the per-step amax is max-reduced over the ranks (see the comment in main())")
     ap.add_argument("--steps", type=int, default=20)
@@ -334,10 +350,25 @@ def main():
     # ---- device-resident timing -------------------------------------------------------------------
     # The K timed steps are captured once into a CUDA graph and replayed, so that microsecond-scale
     # kernels (the 4096^3 GEMM, the GEMV) are not timed behind the Python / ctypes launch path.
+    w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0.record(stream)
     for i in range(args.warmup):
         step(i)
     drain()
+    w1.record(stream)
     barrier()
+    settle_steps = 0
+    if reduce_amax and args.settle_s > 0:
+        # Optional (off by default): untimed steps until the power-capped clocks have settled, to measure the
+        # sustained regime (C2 at N = 2: 0.44 ms per step at 1.41 GHz against 0.35 ms in the first milliseconds).
+        # Every rank derives the same count from the all-reduced warm-up time.
+        t = torch.tensor([w0.elapsed_time(w1) / max(args.warmup, 1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        settle_steps = int(min(8000, args.settle_s * 1e3 / max(float(t.item()), 1e-3)))
+        for i in range(settle_steps):
+            step(i)
+        drain()
+        barrier()
     graph = None
     if not args.no_graph and not reduce_amax:
         cs = torch.cuda.Stream()
@@ -353,7 +384,6 @@ def main():
         graph.replay()          # one untimed replay (also warms the instantiated graph)
         barrier()
     sampler = ClockSampler(local)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     if graph is not None:
@@ -363,6 +393,7 @@ def main():
             step(i)
         drain()
     e1.record(stream)
+    sampler.poll_until(e1)      # the GPU is still working through the timed steps: clocks under load
     barrier()
     ms = e0.elapsed_time(e1)
     inline_aux = None
@@ -397,6 +428,7 @@ def main():
     # ---- end to end: pinned host inputs -> device -> call -> result back --------------------------
     e2e = None
     if not args.no_e2e:
+        sampler.start()          # the end-to-end region is host-paced anyway: a sampling thread runs beside it
         ins, outs = w.io_tensors()
         outs = [t for t in outs if t is not None]
         host_in = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in ins]
@@ -470,8 +502,9 @@ def main():
                "d2h_bytes_per_step": d2h, "ms_per_step": ems / ksteps, "steps": ksteps,
                "pipeline": "2 buffer sets, upload / kernel / read-back on separate streams"}
 
-    sampler.stop_flag = True     # clocks were sampled through both timed regions (device-resident and end-to-end)
-    sampler.join()
+    if sampler.is_alive():       # clocks were sampled through both timed regions (device-resident and end-to-end)
+        sampler.stop_flag = True
+        sampler.join()
 
     def finish():
         """Leave without tearing NCCL down: destroying the process group while an instantiated CUDA graph
@@ -512,6 +545,7 @@ def main():
             cpu["parity_sample"] = parity_sample(w, orc)
 
     if reduce_amax:
+        config["settle_steps_untimed"] = settle_steps
         config["amax_reduce"] = {
             "fused": "every step writes its amax into its own slot; one max-all-reduce over the slots after the last "
                      "step, inside the timed region",
