@@ -350,6 +350,9 @@ def main():
     # ---- device-resident timing -------------------------------------------------------------------
     # The K timed steps are captured once into a CUDA graph and replayed, so that microsecond-scale
     # kernels (the 4096^3 GEMM, the GEMV) are not timed behind the Python / ctypes launch path.
+    # NVML is initialised here, not between the warm-up and the timed steps: the GPUs must not idle there (with a
+    # collective in every step, N GPUs that ramp their clocks up again each at its own pace cost every step)
+    sampler = ClockSampler(local)
     w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     w0.record(stream)
     for i in range(args.warmup):
@@ -383,7 +386,6 @@ def main():
             sptr = sptr_saved
         graph.replay()          # one untimed replay (also warms the instantiated graph)
         barrier()
-    sampler = ClockSampler(local)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     if graph is not None:
