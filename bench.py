@@ -308,9 +308,9 @@ def main():
     #   fused    step i writes its amax into slot i of a vector and ONE all-reduce over the vector follows the last
     #            step -- what delayed-scaling recipes do once per iteration for all their tensors; the per-step
     #            figure is then also timed after the main region and reported beside the value;
-    #   overlap  the reduction of step i runs beside step i + 1 (two slots alternate); slower than inline at N = 2:
-    #            the persistent GEMM sizes its grid to every SM, and a reduction kernel that holds an SM when the
-    #            next GEMM starts delays one of its CTA pairs by a whole round of tiles;
+    #   overlap  the reduction of step i runs beside step i + 1 (two slots alternate); no faster than inline at
+    #            N = 2: the persistent GEMM sizes its grid to every SM, and a reduction kernel that holds an SM
+    #            when the next GEMM starts delays one of its CTA pairs;
     #   off      no reduction (experiments).
     # With a reduction in the step the K steps are launched on the stream, not replayed from a CUDA graph (a step of
     # a third of a millisecond hides the launch path; at N = 8: 0.36 ms per step, 0.35 ms without any reduction).
