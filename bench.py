@@ -41,13 +41,13 @@ if ROOT not in sys.path:
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None where no capture has been taken.
 NCU_TRAFFIC_BYTES = {
-    "c2": 433.8e6,     # profiles/gemm_tc_pair_kernel__c2_hybrid_dgrad.md (full size)
+    "c2": 434.7e6,     # profiles/gemm_tc_pair_kernel__c2_hybrid_dgrad.md (full size)
     "c1": 34.5e6,      # profiles/gemm_tc_pair_kernel__c1_4096cube.md (full size, operands fit L2)
-    "c4": 1962.6e6,    # profiles/gemm_tc_kernel__c4_wgrad_mixed.md (full size)
+    "c4": 1943.0e6,    # profiles/gemm_tc_kernel__c4_wgrad_mixed.md (full size)
     "c3n1": 68.1e6,    # profiles/gemv_async_kernel__c3_batch1.md (full size)
     "c3n8": 67.8e6,    # profiles/gemv_async_kernel__c3_batch8.md
     "c5": 15.65e9,     # profiles/adam_kernel__c5_shrunk8.md: 1.956 GB at 2^27 elements, scaled x8 (traffic is linear in the count)
-    "cast_e4m3_bf16": 3.095e9,   # profiles/cast_kernel__e4m3_to_bf16_shrunk4.md: 773.8 MB at 2^28 elements, scaled x4
+    "cast_e4m3_bf16": 2.994e9,   # profiles/cast_kernel__e4m3_to_bf16_shrunk4.md: 748.4 MB at 2^28 elements, scaled x4
 }
 
 GEMM_LIKE = ("c1", "c2", "c4")
