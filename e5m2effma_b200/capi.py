@@ -49,6 +49,10 @@ def _load():
     lib.e5ma_last_error.argtypes = []
     lib.e5b_gemm_fault.restype = ctypes.c_uint
     lib.e5b_gemm_fault.argtypes = []
+    lib.e5b_set_option.restype = ctypes.c_int
+    lib.e5b_set_option.argtypes = [ctypes.c_char_p, ctypes.c_int]
+    lib.e5b_last_route.restype = ctypes.c_int
+    lib.e5b_last_route.argtypes = []
     lib.e5b_adam_multi.restype = ctypes.c_int
     lib.e5b_adam_multi.argtypes = [ctypes.POINTER(AdamConfig), ctypes.c_int, ctypes.POINTER(ctypes.c_size_t), tp, tp, tp, tp, tp,
                                    ctypes.c_void_p]
@@ -69,6 +73,22 @@ def last_error():
 def gemm_fault():
     """Fault record of the tensor-core GEMM (0 = none); synchronises and clears it."""
     return int(lib.e5b_gemm_fault())
+
+
+ROUTE_NONE, ROUTE_GEMV, ROUTE_GEMV_PERSISTENT, ROUTE_TC_PAIR, ROUTE_TC_PAIR_WIDE, ROUTE_TC_256, ROUTE_TC_128, ROUTE_SIMT, \
+    ROUTE_TC_MIXED_PAIR = range(9)
+
+
+def set_option(name, value):
+    """e5b_set_option: kernel-selection switch `name` (e.g. "TC_PAIR") = value; None or a negative value restores
+    the library's own choice."""
+    if lib.e5b_set_option(name.encode(), -1 if value is None else int(value)) != 0:
+        raise KeyError(f"unknown option {name}")
+
+
+def last_route():
+    """Which kernel the last gemm() call of this thread launched (ROUTE_*)."""
+    return int(lib.e5b_last_route())
 
 
 def tensor(data, dtype, scale_inv=None, scale=None, amax=None, scaling=SCALING_TENSOR):

@@ -9,6 +9,7 @@
 // The hardware converters differ from that only for NaN inputs, which are patched here.
 #pragma once
 #include <stdint.h>
+#include <atomic>
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include "../../include/e5m2effma.h"
@@ -212,8 +213,47 @@ e5ma_status fail(e5ma_status s, const char *fmt, ...) __attribute__((format(prin
 e5ma_status cuda_fail(cudaError_t e, const char *what);   // E5MA_OK when e == cudaSuccess
 
 struct DeviceProps { int cc; int sms; };
+
+// Experiment / test switches of the kernel selection.  Each one starts from its E5MA_* environment variable,
+// which is read once (the first time any switch is asked for); e5b_set_option() changes it afterwards.
+// A negative value means "not set": the library's own choice applies.
+enum Opt {
+  OPT_FORCE_SIMT,     // E5MA_FORCE_SIMT    1: every GEMM runs the ascending-k CUDA-core kernel
+  OPT_TC_PAIR,        // E5MA_TC_PAIR       0: no CTA-pair kernel
+  OPT_TC_SPLIT,       // E5MA_TC_SPLIT      0: the last round of tiles is not cut into slices
+  OPT_TC_GRID,        // E5MA_TC_GRID       n: at most n CTAs in the one-CTA tensor-core kernel
+  OPT_TC_WIDE,        // E5MA_TC_WIDE       0: no wide (256 x up to 512) pair tiles; n >= 256: that tile width
+  OPT_GEMV_KERNEL,    // E5MA_GEMV_KERNEL   0: register loads, 1: cp.async ring, 2: persistent bulk-copy ring
+  OPT_GEMV_STAGES,    // E5MA_GEMV_STAGES   depth of the cp.async ring (2, 3, 4)
+  OPT_GEMV_U,         // E5MA_GEMV_U        k-steps in flight per warp of the register-load kernel
+  OPT_GEMV_MT,        // E5MA_GEMV_MT       2: 32 rows per block in the register-load kernel
+  OPT_MIXED_PAIR,     // E5MA_MIXED_PAIR    0: FP8 x BF16 problems never take the CTA-pair kernel
+  OPT_COUNT
+};
+int opt(Opt which);
+
+// Which kernel the last e5ma_gemm call of this host thread launched (e5b_last_route()).
+enum Route { ROUTE_NONE = 0, ROUTE_GEMV = 1, ROUTE_GEMV_PERSISTENT = 2, ROUTE_TC_PAIR = 3, ROUTE_TC_PAIR_WIDE = 4,
+             ROUTE_TC_256 = 5, ROUTE_TC_128 = 6, ROUTE_SIMT = 7, ROUTE_TC_MIXED_PAIR = 8 };
+void note_route(int r);
 // E5MA_OK and the properties of the current device when it is compute capability 10.x
 e5ma_status require_blackwell(const char *who, DeviceProps *out);
+
+// Opt-in to more than 48 KiB of dynamic shared memory, once per kernel and device.  One object per kernel
+// (a function-local static of the launcher); safe when several host threads launch at once.
+struct SmemOptIn {
+  std::atomic<unsigned char> done[64];
+  template <typename K>
+  cudaError_t ensure(K kernel, int bytes) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::atomic<unsigned char> &d = done[dev & 63];
+    if (d.load(std::memory_order_acquire)) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) d.store(1, std::memory_order_release);
+    return e;
+  }
+};
 
 // kernel launchers implemented in the other translation units
 cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx,

@@ -8,6 +8,9 @@
 #include <stdarg.h>
 #include <stdio.h>
 #include <atomic>
+#include <mutex>
+#include <stdlib.h>
+#include <string.h>
 #include "common.cuh"
 
 namespace e5b {
@@ -28,6 +31,32 @@ e5ma_status cuda_fail(cudaError_t e, const char *what) {
   if (e == cudaSuccess) return E5MA_OK;
   return fail(E5MA_CUDA_ERROR, "%s: CUDA error %d (%s): %s", what, (int)e, cudaGetErrorName(e), cudaGetErrorString(e));
 }
+
+// ---- switches and the route record ----------------------------------------------------------------
+static std::atomic<int> g_opt[OPT_COUNT];
+static const char *const kOptNames[OPT_COUNT] = {"FORCE_SIMT", "TC_PAIR", "TC_SPLIT", "TC_GRID", "TC_WIDE", "GEMV_KERNEL",
+                                                 "GEMV_STAGES", "GEMV_U", "GEMV_MT", "MIXED_PAIR"};
+static void opt_init() {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    for (int i = 0; i < OPT_COUNT; ++i) {
+      char name[48];
+      snprintf(name, sizeof name, "E5MA_%s", kOptNames[i]);
+      const char *e = getenv(name);
+      g_opt[i].store(e && e[0] ? atoi(e) : -1, std::memory_order_relaxed);
+    }
+    // the older spelling of the GEMV switch: E5MA_GEMV_ASYNC=0 meant the register-load kernel
+    if (g_opt[OPT_GEMV_KERNEL].load() < 0)
+      if (const char *e = getenv("E5MA_GEMV_ASYNC")) g_opt[OPT_GEMV_KERNEL].store(atoi(e) ? 1 : 0);
+  });
+}
+int opt(Opt which) {
+  opt_init();
+  return g_opt[which].load(std::memory_order_relaxed);
+}
+
+static thread_local int t_route = ROUTE_NONE;
+void note_route(int r) { t_route = r; }
 
 // Per-device cache; entries are written once (two threads racing write the same values) and
 // published through the atomic flag.
@@ -187,6 +216,31 @@ __global__ void __launch_bounds__(256) cast_kernel(const void *__restrict__ src,
   if (amax) block_amax(amax, mx);
 }
 
+// Source and destination overlap (an in-place cast between dtypes of one size, or a same-dtype "copy + amax"
+// onto itself): element by element through ordinary, coherent accesses -- the kernel above reads through the
+// non-coherent path and promises the compiler that the two arrays do not alias.  Element i is read and then
+// written by the same thread, so an exact in-place cast is well defined; partial overlaps are the caller's
+// business, as in the reference (src/e5m2effma.cu:85-101 checks nothing).
+__global__ void __launch_bounds__(256) cast_alias_kernel(int ts, int td, const void *src, void *dst, size_t count,
+                                                         const float *sinv_p, const float *scale_p, float *amax) {
+  const float sinv = ld_or_one(sinv_p), qs = ld_or_one(scale_p);
+  float mx = 0.f;
+  const size_t nthr = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += nthr) {
+    float v;
+    switch (ts) {
+      case E5MA_E5M2: v = __fmul_rn(dec_e5m2(((const volatile uint8_t *)src)[i]), sinv); break;
+      case E5MA_E4M3: v = __fmul_rn(dec_e4m3(((const volatile uint8_t *)src)[i]), sinv); break;
+      case E5MA_BF16: v = dec_bf16(((const volatile uint16_t *)src)[i]); break;
+      case E5MA_FP16: v = f16bits_to_f32(((const volatile uint16_t *)src)[i]); break;
+      default: v = ((const volatile float *)src)[i];
+    }
+    mx = fmaxf(mx, fabsf(v));
+    store_elem(td, dst, i, v, qs);
+  }
+  if (amax) block_amax(amax, mx);
+}
+
 template <int TS, int TD>
 static cudaError_t cast_launch(const void *src, void *dst, size_t count, const float *sinv, const float *scale,
                                float *amax, int sms, cudaStream_t s) {
@@ -219,6 +273,21 @@ static cudaError_t cast_dst(int td, const void *src, void *dst, size_t count, co
 
 extern "C" const char *e5ma_last_error(void) { return e5b::t_error; }
 
+extern "C" int e5b_set_option(const char *name, int value) {
+  using namespace e5b;
+  if (!name) return -1;
+  opt_init();
+  if (!strncmp(name, "E5MA_", 5)) name += 5;
+  for (int i = 0; i < OPT_COUNT; ++i)
+    if (!strcmp(name, kOptNames[i])) {
+      g_opt[i].store(value < 0 ? -1 : value, std::memory_order_relaxed);
+      return 0;
+    }
+  return -1;
+}
+
+extern "C" int e5b_last_route(void) { return e5b::t_route; }
+
 extern "C" const char *e5ma_status_string(e5ma_status s) {
   switch (s) {
     case E5MA_OK: return "E5MA_OK";
@@ -244,6 +313,15 @@ extern "C" e5ma_status e5ma_cast(const e5ma_tensor *src, const e5ma_tensor *dst,
   const float *sinv = is_fp8(src->dtype) ? src->scale_inv : nullptr;
   const float *scale = is_fp8(dst->dtype) ? dst->scale : nullptr;
   cudaError_t err;
+  const uintptr_t s0 = (uintptr_t)src->data, s1 = s0 + count * elem_bytes(src->dtype);
+  const uintptr_t d0 = (uintptr_t)dst->data, d1 = d0 + count * elem_bytes(dst->dtype);
+  if (s0 < d1 && d0 < s1) {   // overlapping buffers
+    size_t blocks = (count + 255) / 256;
+    if (blocks > (size_t)dp.sms * 16) blocks = (size_t)dp.sms * 16;
+    cast_alias_kernel<<<(unsigned)blocks, 256, 0, stream>>>(src->dtype, dst->dtype, src->data, dst->data, count, sinv, scale,
+                                                            dst->amax);
+    return cuda_fail(cudaGetLastError(), "e5ma_cast: kernel launch");
+  }
   switch (src->dtype) {
     case E5MA_E4M3: err = cast_dst<E5MA_E4M3>(dst->dtype, src->data, dst->data, count, sinv, scale, dst->amax, dp.sms, stream); break;
     case E5MA_BF16: err = cast_dst<E5MA_BF16>(dst->dtype, src->data, dst->data, count, sinv, scale, dst->amax, dp.sms, stream); break;

@@ -146,14 +146,16 @@ extern "C" e5ma_status e5ma_gemm(e5ma_op transa, e5ma_op transb, int m, int n, i
 
   const uint8_t *a = (const uint8_t *)A->data, *b = (const uint8_t *)B->data;
   cudaError_t err = cudaErrorNotSupported;
-  // E5MA_FORCE_SIMT=1 (experiments and tests): every problem takes the ascending-k CUDA-core kernel
-  const char *force = getenv("E5MA_FORCE_SIMT");
-  if (force && force[0] == '1') { /* keep err: falls through to the CUDA-core kernel */ }
+  // switch FORCE_SIMT (experiments and tests): every problem takes the ascending-k CUDA-core kernel
+  note_route(ROUTE_NONE);
+  if (opt(OPT_FORCE_SIMT) == 1) { /* keep err: falls through to the CUDA-core kernel */ }
   else if (n <= 8 && a_kc && b_kc && is_fp8(A->dtype) && B->dtype != E5MA_FP32 && k > 0)
     err = launch_gemv_mma(A->dtype, B->dtype, a, lda, b, ldb, m, n, k, o, dp.sms, stream);
   else if (A->dtype != E5MA_FP32 && B->dtype != E5MA_FP32 && k > 0)
     err = launch_gemm_tc(A->dtype, B->dtype, a_kc, b_kc, a, lda, b, ldb, m, n, k, o, dp.sms, stream);
-  if (err == cudaErrorNotSupported)
+  if (err == cudaErrorNotSupported) {
+    note_route(ROUTE_SIMT);
     err = launch_gemm_simt(A->dtype, B->dtype, a_kc, b_kc, a, lda, b, ldb, m, n, k, o, stream);
+  }
   return cuda_fail(err, "e5ma_gemm: kernel launch");
 }

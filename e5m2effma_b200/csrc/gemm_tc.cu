@@ -285,21 +285,13 @@ static cudaError_t launch_cfg(const CUtensorMap &mi, const CUtensorMap &mj, cons
                               int k_bytes, uint32_t idesc, uint32_t idesc_half, const OutDesc &o, const EpiMode &md, int sms,
                               cudaStream_t s) {
   using C = Cfg<BI, CONV>;
-  static bool attr_done[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_done[dev & 63]) {
-    const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BI, KIND, DT, CONV, FT>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    attr_done[dev & 63] = true;
-  }
+  static SmemOptIn optin;
+  if (const cudaError_t e = optin.ensure(gemm_tc_kernel<BI, KIND, DT, CONV, FT>, C::SMEM_BYTES)) return e;
   const int tiles = ((m + BI - 1) / BI) * ((n + BM - 1) / BM);
   int grid = tiles < sms ? tiles : sms;
-  if (const char *g = getenv("E5MA_TC_GRID")) {   // experiments: fewer CTAs than SMs
-    const int v = atoi(g);
-    if (v > 0 && v < grid) grid = v;
-  }
+  const int cap = opt(OPT_TC_GRID);   // experiments: fewer CTAs than SMs
+  if (cap > 0 && cap < grid) grid = cap;
+  note_route(BI == 256 ? ROUTE_TC_256 : ROUTE_TC_128);
   gemm_tc_kernel<BI, KIND, DT, CONV, FT><<<grid, C::NTHREADS, C::SMEM_BYTES, s>>>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md);
   return cudaGetLastError();
 }
@@ -346,8 +338,7 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   const int kind = f8 ? 0 : 1;
   const int ft = conv == 1 ? a_dtype : (conv == 2 ? b_dtype : E5MA_E5M2);
   // CTA pairs (gemm_tc2.cuh) for big unmixed problems: 256 x 256 tiles, half the operand bytes per CTA
-  int use_pair = 1;
-  if (const char *e = getenv("E5MA_TC_PAIR")) use_pair = atoi(e);   // experiments: 0 keeps every problem on single CTAs
+  const bool use_pair = opt(OPT_TC_PAIR) != 0;   // experiments: 0 keeps every problem on single CTAs
   if (use_pair && a_kc && b_kc && conv == 0 && m >= 512 && n >= 512 && ((m + 255) / 256) * ((n + 255) / 256) >= sms / 2) {
     CUtensorMap pi, pj, pi2, pi4;
     if (!make_map(&pi, A, elem_bytes(a_dtype), k, m, lda, 128, false) ||
@@ -360,8 +351,7 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
       return ((uintptr_t)p & 15u) == 0 && ((size_t)ld * elem_bytes(dtype)) % 16 == 0;
     };
     EpiMode pm = {};
-    pm.split = 1;
-    if (const char *e = getenv("E5MA_TC_SPLIT")) pm.split = atoi(e);
+    pm.split = opt(OPT_TC_SPLIT) != 0;
     pm.vec = vec_ok2(o.d, o.ldd, o.d_dtype);
     if (o.c && !((o.c_dtype == E5MA_FP32 || o.c_dtype == E5MA_BF16) && vec_ok2(o.c, o.ldc, o.c_dtype))) pm.vec = 0;
     if (o.bias && !((o.bias_dtype == E5MA_FP32 || o.bias_dtype == E5MA_BF16) && ((uintptr_t)o.bias & 15u) == 0)) pm.vec = 0;
@@ -401,8 +391,7 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   md.transposed = tr ? 1 : 0;
   md.mn_n = n_kc ? 0 : 1;
   md.mn_m = m_kc ? 0 : 1;
-  md.split = wide ? 1 : 0;
-  if (const char *e = getenv("E5MA_TC_SPLIT")) md.split = atoi(e) && wide;   // experiments
+  md.split = wide && opt(OPT_TC_SPLIT) != 0;
   md.vec = vec_ok(o.d, o.ldd, o.d_dtype);
   if (o.c && !((o.c_dtype == E5MA_FP32 || o.c_dtype == E5MA_BF16) && vec_ok(o.c, o.ldc, o.c_dtype))) md.vec = 0;
   if (o.bias && !((o.bias_dtype == E5MA_FP32 || o.bias_dtype == E5MA_BF16) && ((uintptr_t)o.bias & 15u) == 0)) md.vec = 0;
@@ -413,10 +402,12 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
 
 }  // namespace e5b
 
-// Reads and clears the fault word of the tensor-core GEMM on the current device (synchronises).
+// Reads and clears the fault word of the tensor-core GEMM on the current device.  Waits for the whole device
+// first: a copy from a symbol on the legacy stream would not wait for work on non-blocking streams.
 // 0: no bounded wait ever ran out.  Declared in include/e5m2effma_b200.h.
 extern "C" unsigned int e5b_gemm_fault(void) {
   unsigned int v = 0, zero = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return 0xFFFFFFFFu;
   if (cudaMemcpyFromSymbol(&v, e5b::tc::g_fault, sizeof v) != cudaSuccess) return 0xFFFFFFFFu;
   cudaMemcpyToSymbol(e5b::tc::g_fault, &zero, sizeof zero);
   return v;

@@ -261,15 +261,9 @@ template <int KIND, int DT>
 static cudaError_t launch_pair_cfg(const CUtensorMap &mi, const CUtensorMap &mj, const CUtensorMap &mi2, const CUtensorMap &mi4,
                                    int m, int n, int k_bytes, uint32_t idesc, const PairSplit &ps, const OutDesc &o,
                                    const EpiMode &md, int sms, cudaStream_t s) {
-  static bool attr_done[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!attr_done[dev & 63]) {
-    const cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<KIND, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               P_SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    attr_done[dev & 63] = true;
-  }
+  static SmemOptIn optin;
+  if (const cudaError_t e = optin.ensure(gemm_tc_pair_kernel<KIND, DT>, P_SMEM_BYTES)) return e;
+  note_route(ROUTE_TC_PAIR);
   const int tiles = ((m + P_TILE - 1) / P_TILE) * ((n + P_TILE - 1) / P_TILE);
   int pairs = sms / 2;
   if (tiles < pairs) pairs = tiles;

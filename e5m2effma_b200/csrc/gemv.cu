@@ -266,16 +266,10 @@ static cudaError_t gemv_async_x(int x_dtype, const uint8_t *A, int lda, const ui
                                 const OutDesc &o, cudaStream_t s) {
   constexpr int GA_SMEM = GV_WARPS * GA_STAGES * 2048;
   const unsigned grid = (unsigned)((m + 15) / 16);
-  static bool attr_done[3][64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
 #define E5B_GEMV_CASE(XT, slot_)                                                                                            \
   {                                                                                                                         \
-    if (!attr_done[slot_][dev & 63]) {                                                                                      \
-      const cudaError_t e = cudaFuncSetAttribute(gemv_async_kernel<AT, XT, GA_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, GA_SMEM); \
-      if (e != cudaSuccess) return e;                                                                                       \
-      attr_done[slot_][dev & 63] = true;                                                                                    \
-    }                                                                                                                       \
+    static SmemOptIn optin;                                                                                                 \
+    if (const cudaError_t e = optin.ensure(gemv_async_kernel<AT, XT, GA_STAGES>, GA_SMEM)) return e;                        \
     gemv_async_kernel<AT, XT, GA_STAGES><<<grid, GV_WARPS * 32, GA_SMEM, s>>>(A, lda, X, ldx, m, n, k, o);                             \
   }
   switch (x_dtype) {
@@ -306,7 +300,7 @@ template <int MT, int AT>
 static cudaError_t gemv_x(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
                           const OutDesc &o, cudaStream_t s) {
   int u = 1;   // measured on B200: one k-step per warp in flight (more registers cost occupancy and lose)
-  if (const char *e = getenv("E5MA_GEMV_U")) u = atoi(e);
+  if (opt(OPT_GEMV_U) > 0) u = opt(OPT_GEMV_U);
   if (u >= 4 && MT == 1) return gemv_xu<MT, AT, MT == 1 ? 4 : 2>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
   if (u >= 2) return gemv_xu<MT, AT, 2>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
   return gemv_xu<MT, AT, 1>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
@@ -317,13 +311,13 @@ static cudaError_t gemv_x(int x_dtype, const uint8_t *A, int lda, const uint8_t 
 cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx,
                             int m, int n, int k, const OutDesc &o, int sms, cudaStream_t s) {
   // Measured on B200 (8192 x 8192 weights, batch 1 / 8): the cp.async pipeline with X prefetched one step
-  // ahead takes 15.2 / 15.8 us, the register-load kernel 15.8 / 16.6 us.  E5MA_GEMV_ASYNC=0 (experiments)
-  // selects the latter.
-  bool use_async = true;
-  if (const char *e = getenv("E5MA_GEMV_ASYNC")) use_async = atoi(e) != 0;
+  // ahead takes 15.2 / 15.8 us, the register-load kernel 15.8 / 16.6 us.  the GEMV_KERNEL switch = 0
+  // (experiments) selects the latter.
+  const bool use_async = opt(OPT_GEMV_KERNEL) != 0;
+  note_route(ROUTE_GEMV);
   if (use_async) {
     int stages = 2;   // 32 KiB per block: every row tile of an 8192-row matrix is resident in one wave
-    if (const char *e = getenv("E5MA_GEMV_STAGES")) stages = atoi(e);
+    if (opt(OPT_GEMV_STAGES) > 0) stages = opt(OPT_GEMV_STAGES);
     if (a_dtype == E5MA_E5M2)
       return stages == 2 ? gemv_async_x<E5MA_E5M2, 2>(x_dtype, A, lda, X, ldx, m, n, k, o, s)
            : stages == 4 ? gemv_async_x<E5MA_E5M2, 4>(x_dtype, A, lda, X, ldx, m, n, k, o, s)
@@ -336,7 +330,7 @@ cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda,
   }
   bool wide = false;   // measured on B200: 16 rows per block wins for every n <= 8 (more blocks, fewer registers)
   (void)sms;
-  if (const char *e = getenv("E5MA_GEMV_MT")) wide = atoi(e) == 2;   // experiments
+  wide = opt(OPT_GEMV_MT) == 2;   // experiments
   if (a_dtype == E5MA_E5M2)
     return wide ? gemv_x<2, E5MA_E5M2>(x_dtype, A, lda, X, ldx, m, n, k, o, s)
                 : gemv_x<1, E5MA_E5M2>(x_dtype, A, lda, X, ldx, m, n, k, o, s);

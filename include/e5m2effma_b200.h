@@ -11,10 +11,28 @@ extern "C" {
 
 /* Diagnostic of the tensor-core GEMM.  Its kernels wait on hardware barriers with a time limit;
  * a wait that runs out makes the kernel give up cleanly (tensor memory released, no hang) and
- * record which role waited for what.  This call synchronises the current device's default
- * context, returns that record (0 = no wait ever ran out) and clears it.
+ * record which role waited for what; e5ma_gemm has returned E5MA_OK long before, and D is then
+ * undefined.  This call waits for all work of the current device (cudaDeviceSynchronize), returns
+ * that record (0 = no wait ever ran out) and clears it.  A caller that needs certainty polls it
+ * after the GEMMs it cares about.
  * No counterpart in the reference, whose kernels have no waits. */
 unsigned int e5b_gemm_fault(void);
+
+/* Kernel-selection switches for experiments, the tuner and the tests.  name is one of FORCE_SIMT,
+ * TC_PAIR, TC_SPLIT, TC_GRID, TC_WIDE, GEMV_KERNEL, GEMV_STAGES, GEMV_U, GEMV_MT, MIXED_PAIR (an
+ * "E5MA_" prefix is accepted); each starts from the environment variable E5MA_<name>, read once per
+ * process.  value < 0 restores the library's own choice.  Returns 0, or -1 for an unknown name.
+ * Process-wide; not meant to be flipped while other threads are inside e5ma_gemm.
+ * Takes the place of rebuilding the reference with another tuned table (src/e5m2effma_tuned.h). */
+int e5b_set_option(const char *name, int value);
+
+/* Which kernel the last e5ma_gemm call of the calling host thread launched: 0 none (rejected, or
+ * m == 0 / n == 0), 1 streaming GEMV, 2 persistent GEMV, 3 CTA-pair tensor-core GEMM (256 x 256
+ * tiles), 4 the same with wide tiles (256 x up to 512), 5 / 6 one-CTA tensor-core GEMM with
+ * 256 x 128 / 128 x 128 tiles, 7 ascending-k CUDA-core GEMM, 8 CTA-pair GEMM for FP8 x BF16 pairs.
+ * The tests use it to assert that a case really ran on the kernel it was written for.
+ * No counterpart in the reference (one GEMM kernel, one GEMV kernel). */
+int e5b_last_route(void);
 
 /* One Adam / AdamW step (the arithmetic of e5ma_adam, same cfg) over a list of num_tensors tensors in as
  * few launches as possible: up to 24 tensors share a launch, each block of the grid works on one

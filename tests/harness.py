@@ -209,10 +209,8 @@ def check_tolerance(data: GemmData, got, amax):
 
 
 def force_simt(on):
-    if on:
-        os.environ["E5MA_FORCE_SIMT"] = "1"
-    else:
-        os.environ.pop("E5MA_FORCE_SIMT", None)
+    from e5m2effma_b200 import capi
+    capi.set_option("FORCE_SIMT", 1 if on else None)
 
 
 def reference_gemm_cases():

@@ -22,8 +22,9 @@ def test_every_declared_symbol_is_exported():
     names = set()
     for fn in os.listdir(os.path.join(ROOT, "include")):
         text = open(os.path.join(ROOT, "include", fn)).read()
-        names |= set(re.findall(r"\b(e5ma_[a-z_0-9]+)\s*\(", text))
-    assert {"e5ma_gemm", "e5ma_cast", "e5ma_adam", "e5ma_status_string", "e5ma_last_error"} <= names
+        names |= set(re.findall(r"\b(e5(?:ma|b)_[a-z_0-9]+)\s*\(", text))
+    assert {"e5ma_gemm", "e5ma_cast", "e5ma_adam", "e5ma_status_string", "e5ma_last_error", "e5b_gemm_fault",
+            "e5b_adam_multi", "e5b_set_option", "e5b_last_route"} <= names
     for n in names:
         assert hasattr(capi.lib, n), n
 
@@ -131,3 +132,17 @@ def test_adam_multi_rejects():
     assert "differs in dtype" in capi.last_error()
     assert capi.adam_multi(cfg, [8], [T(capi.FP32, data=None)], [f32], [f32], [f32]) == capi.INVALID_VALUE
     assert capi.adam_multi(cfg, [], [], [], [], []) == capi.OK and capi.last_error() == ""
+
+
+def test_options_and_route_record():
+    """e5b_set_option knows every documented switch (with or without the E5MA_ prefix), rejects others, and the
+    route record starts at 'none' and stays there for calls that launch nothing."""
+    for name in ["FORCE_SIMT", "TC_PAIR", "TC_SPLIT", "TC_GRID", "TC_WIDE", "GEMV_KERNEL", "GEMV_STAGES", "GEMV_U",
+                 "GEMV_MT", "MIXED_PAIR", "E5MA_TC_PAIR"]:
+        capi.set_option(name, 1)
+        capi.set_option(name, None)
+    with pytest.raises(KeyError):
+        capi.set_option("NO_SUCH_SWITCH", 1)
+    t = capi.tensor(16, capi.E5M2)
+    assert capi.gemm(capi.OP_T, capi.OP_N, 0, 4, 16, 1.0, t, 16, t, 16, 0.0, None, 0, capi.tensor(16, capi.BF16), 1, None) == capi.OK
+    assert capi.last_route() == capi.ROUTE_NONE
