@@ -111,3 +111,28 @@ def test_small_counts(n):
     got, amax = gpu_cast(x, FP32, E4M3, n, None, 2.0)
     exp, eamax = orc.cast(x, FP32, E4M3, None, 2.0, amax=0.0)
     assert np.array_equal(got, exp) and amax == eamax
+
+
+@pytest.mark.parametrize("sdt,ddt", [(BF16, BF16), (E4M3, E5M2), (E5M2, E5M2), (BF16, FP16), (FP32, FP32)])
+def test_in_place_cast_between_dtypes_of_one_size(sdt, ddt):
+    """src == dst: the reference allows it (same-dtype casts act as copy + amax, src/e5m2effma.cu:85-101 checks no
+    overlap); the result must be what the out-of-place cast gives."""
+    import torch
+    from e5m2effma_b200 import capi
+    rng = np.random.default_rng(7 * sdt + ddt)
+    n = (1 << 18) + 21
+    src = source(sdt, n, rng)
+    si = 0.5 if is_fp8(sdt) else None
+    sc = 2.0 if is_fp8(ddt) else None
+    exp, eamax = orc.cast(src, sdt, ddt, si, sc, amax=0.0)
+    buf, p = to_dev(src)
+    keep = [to_dev(np.array([v], np.float32)) for v in (si or 1.0, sc or 1.0, 0.0)]
+    S = capi.tensor(p, sdt, keep[0][1])
+    D = capi.tensor(p, ddt, None, keep[1][1], keep[2][1])
+    st = capi.cast(S, D, n, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert st == capi.OK, capi.last_error()
+    got = from_dev(buf, orc.NP_STORAGE[ddt], n)
+    amax = from_dev(keep[2][0], np.float32, 1)[0]
+    assert same(ddt, got, exp)
+    assert amax == eamax or (np.isnan(amax) and np.isnan(eamax))
