@@ -7,8 +7,16 @@ functional interface of the reference's binding (binds/python/e5m2effma/__init__
 memory and streams only.  There is no CPU path and no alternative backend: a missing library or
 a GPU other than compute capability 10.0 raises.
 """
-from . import capi
-from .functional import AdamW, adam_step, adam_step_multi, cast, get_include, linear, matmul
-
 __version__ = "0.2.0"
 __all__ = ["capi", "matmul", "linear", "cast", "adam_step", "adam_step_multi", "AdamW", "get_include", "__version__"]
+
+
+def __getattr__(name):
+    """The binding (and with it libe5m2effma.so) is loaded on first use of any public name."""
+    if name == "capi":
+        import importlib
+        return importlib.import_module(".capi", __name__)
+    if name in __all__:
+        from . import functional
+        return getattr(functional, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

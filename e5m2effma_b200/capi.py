@@ -49,6 +49,8 @@ def _load():
     lib.e5ma_last_error.argtypes = []
     lib.e5b_gemm_fault.restype = ctypes.c_uint
     lib.e5b_gemm_fault.argtypes = []
+    lib.e5b_gemm_bcast.restype = ctypes.c_int
+    lib.e5b_gemm_bcast.argtypes = lib.e5ma_gemm.argtypes[:-1] + [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
     lib.e5b_set_option.restype = ctypes.c_int
     lib.e5b_set_option.argtypes = [ctypes.c_char_p, ctypes.c_int]
     lib.e5b_last_route.restype = ctypes.c_int
@@ -104,6 +106,13 @@ def gemm(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, b
     """e5ma_gemm; tensors are capi.Tensor (or None); returns the e5ma_status."""
     return lib.e5ma_gemm(transa, transb, m, n, k, alpha, _ref(A), lda, _ref(B), ldb, beta, _ref(C), ldc, _ref(D), ldd,
                          _ref(bias), stream)
+
+
+def gemm_bcast(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, bias, peers, stream=0):
+    """e5b_gemm_bcast: e5ma_gemm that also stores D into the buffers whose device addresses are listed in `peers`."""
+    arr = (ctypes.c_void_p * max(len(peers), 1))(*peers)
+    return lib.e5b_gemm_bcast(transa, transb, m, n, k, alpha, _ref(A), lda, _ref(B), ldb, beta, _ref(C), ldc, _ref(D), ldd,
+                              _ref(bias), len(peers), arr, stream)
 
 
 def cast(src, dst, count, stream=0):

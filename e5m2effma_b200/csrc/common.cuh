@@ -168,6 +168,7 @@ __device__ __forceinline__ void block_amax(float *amax, float m) {
 }
 
 // ---- output description of GEMM / GEMV (reference include/e5m2effma.h:27-31) -------------------
+constexpr int MAX_PEERS = 7;   // other GPUs of an 8-GPU node
 struct OutDesc {
   const float *sa, *sb;   // scale_inv of FP8 A / B (NULL: 1)
   int sa_vec, sb_vec;     // 1: one factor per row i / per column j
@@ -176,6 +177,9 @@ struct OutDesc {
   void *d; int ldd, d_dtype; const float *d_scale;
   float *amax;
   const void *bias; int bias_dtype;
+  // e5b_gemm_bcast: every output element is also stored at the same element offset of these buffers (other GPUs'
+  // copies of D, mapped into this device's address space); plain stores, no reads
+  int npeers; void *peer[MAX_PEERS];
 };
 
 struct OutScalars { float s, qs, csinv; };   // per-tensor factors read once per thread
@@ -204,6 +208,7 @@ __device__ __forceinline__ float out_value(const OutDesc &o, const OutScalars &r
 __device__ __forceinline__ float out_store(const OutDesc &o, const OutScalars &r, int i, int j, float acc) {
   const float v = out_value(o, r, i, j, acc);
   store_elem(o.d_dtype, o.d, (size_t)j * o.ldd + i, v, r.qs);
+  for (int p = 0; p < o.npeers; ++p) store_elem(o.d_dtype, o.peer[p], (size_t)j * o.ldd + i, v, r.qs);
   return fabsf(v);
 }
 
@@ -260,6 +265,7 @@ cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda,
                             int m, int n, int k, const OutDesc &o, int sms, cudaStream_t s);
 cudaError_t launch_gemm_simt(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const uint8_t *A, int lda,
                              const uint8_t *B, int ldb, int m, int n, int k, const OutDesc &o, cudaStream_t s);
+unsigned int gemv_fault_read_and_clear();   // fault word of the persistent GEMV's bounded waits (after a device sync)
 // returns cudaErrorNotSupported when the problem is outside what the tensor-core kernel takes
 cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const uint8_t *A, int lda,
                            const uint8_t *B, int ldb, int m, int n, int k, const OutDesc &o, int sms,

@@ -80,11 +80,10 @@ cudaError_t launch_gemm_simt(int a_dtype, int b_dtype, bool a_kc, bool b_kc, con
 
 }  // namespace e5b
 
-extern "C" e5ma_status e5ma_gemm(e5ma_op transa, e5ma_op transb, int m, int n, int k, float alpha,
-                                 const e5ma_tensor *A, int lda, const e5ma_tensor *B, int ldb, float beta,
-                                 const e5ma_tensor *C, int ldc, const e5ma_tensor *D, int ldd,
-                                 const e5ma_tensor *bias, cudaStream_t stream) {
-  using namespace e5b;
+namespace e5b {
+static e5ma_status gemm_impl(e5ma_op transa, e5ma_op transb, int m, int n, int k, float alpha, const e5ma_tensor *A, int lda,
+                             const e5ma_tensor *B, int ldb, float beta, const e5ma_tensor *C, int ldc, const e5ma_tensor *D,
+                             int ldd, const e5ma_tensor *bias, int num_peers, void *const *peer_d, cudaStream_t stream) {
   clear_error();
   const auto known = [](const e5ma_tensor *t) { return t->dtype >= E5MA_E4M3 && t->dtype <= E5MA_E5M2; };
   const auto operand_type = [](int t) { return is_fp8(t) || t == E5MA_BF16 || t == E5MA_FP32; };
@@ -143,6 +142,8 @@ extern "C" e5ma_status e5ma_gemm(e5ma_op transa, e5ma_op transb, int m, int n, i
   o.amax = D->amax;
   o.bias = has_bias ? bias->data : nullptr;
   o.bias_dtype = has_bias ? (int)bias->dtype : E5MA_FP32;
+  o.npeers = num_peers;
+  for (int p = 0; p < MAX_PEERS; ++p) o.peer[p] = p < num_peers ? peer_d[p] : nullptr;
 
   const uint8_t *a = (const uint8_t *)A->data, *b = (const uint8_t *)B->data;
   cudaError_t err = cudaErrorNotSupported;
@@ -158,4 +159,31 @@ extern "C" e5ma_status e5ma_gemm(e5ma_op transa, e5ma_op transb, int m, int n, i
     err = launch_gemm_simt(A->dtype, B->dtype, a_kc, b_kc, a, lda, b, ldb, m, n, k, o, stream);
   }
   return cuda_fail(err, "e5ma_gemm: kernel launch");
+}
+}  // namespace e5b
+
+extern "C" e5ma_status e5ma_gemm(e5ma_op transa, e5ma_op transb, int m, int n, int k, float alpha,
+                                 const e5ma_tensor *A, int lda, const e5ma_tensor *B, int ldb, float beta,
+                                 const e5ma_tensor *C, int ldc, const e5ma_tensor *D, int ldd,
+                                 const e5ma_tensor *bias, cudaStream_t stream) {
+  return e5b::gemm_impl(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, bias, 0, nullptr, stream);
+}
+
+// e5ma_gemm whose epilogue also stores every output into other GPUs' copies of D (declared in
+// include/e5m2effma_b200.h).  Argument checks of its own first, then those of e5ma_gemm in their usual order.
+extern "C" e5ma_status e5b_gemm_bcast(e5ma_op transa, e5ma_op transb, int m, int n, int k, float alpha,
+                                      const e5ma_tensor *A, int lda, const e5ma_tensor *B, int ldb, float beta,
+                                      const e5ma_tensor *C, int ldc, const e5ma_tensor *D, int ldd,
+                                      const e5ma_tensor *bias, int num_peers, void *const *peer_d, cudaStream_t stream) {
+  using namespace e5b;
+  clear_error();
+  if (num_peers < 0 || num_peers > MAX_PEERS)
+    return fail(E5MA_INVALID_VALUE, "e5b_gemm_bcast: num_peers = %d, must be 0..%d", num_peers, MAX_PEERS);
+  if (num_peers > 0 && !peer_d) return fail(E5MA_INVALID_VALUE, "e5b_gemm_bcast: peer_d is NULL");
+  for (int p = 0; p < num_peers; ++p) {
+    if (!peer_d[p]) return fail(E5MA_INVALID_VALUE, "e5b_gemm_bcast: peer_d[%d] is NULL", p);
+    if (D && D->data && (((uintptr_t)peer_d[p] ^ (uintptr_t)D->data) & 15u))
+      return fail(E5MA_INVALID_VALUE, "e5b_gemm_bcast: peer_d[%d] must have the alignment of D (mod 16 bytes)", p);
+  }
+  return gemm_impl(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, D, ldd, bias, num_peers, peer_d, stream);
 }

@@ -41,6 +41,7 @@
 // tensor memory is released.  e5b_gemm_fault() reads the word back.
 #include "tc_common.cuh"
 #include "gemm_tc2.cuh"
+#include "gemm_tc3.cuh"
 
 namespace e5b {
 namespace tc {
@@ -321,6 +322,61 @@ static cudaError_t launch_kind(int kind, int conv, int ft, const CUtensorMap &mi
 
 }  // namespace tc
 
+// ---- choice between the pair kernels -----------------------------------------------------------------
+// A small cost model in SM clocks, fitted to measurements on B200.  The FP8 mainloop is power-bound there: the
+// 256 x 256 pair kernel, the wide-tile pair kernel (25 % fewer operand bytes per FLOP) and the one-CTA kernel
+// (50 % more) all retire a 256 x 256 x 128-byte k-block per SM pair in about 712 clocks where its MMAs need 512 --
+// under ncu the wide kernel shows a higher SM clock and a proportionally less busy tensor pipe, the product is
+// the same.  So a k-block costs 2.78 clocks per tile row whatever the kernel, and what differs between the
+// plans is how the tiles fill the rounds over the SM pairs and which epilogues are exposed: the wide kernel
+// pays its epilogue after every tile, the double-buffered ones only after the last.  The 256 x 256 kernel
+// carries an empirical 5 % (it measures that much slower than the model on long-K problems).
+struct PairPlan { int W; double clocks; bool wide; };
+
+static double kblock_clocks(int w) { return 2.78 * w; }
+static double epilogue_clocks(int w) { return 1500.0 + 5.0 * w; }
+
+static double pair_clocks(int m, int n, int kblocks, int W, bool wide, int sms) {
+  const int tiles = ((m + W - 1) / W) * ((n + 255) / 256);
+  int pairs = sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  const int rounds = tiles / pairs, rest = tiles % pairs;
+  int f = 1;
+  if (rest > 0 && opt(OPT_TC_SPLIT) != 0) {
+    if (wide) f = tc::wide_plan(W, tiles, pairs).slices;
+    else f = 4 * rest <= pairs ? 4 : (2 * rest <= pairs ? 2 : 1);
+  }
+  double c = rounds * (kblocks * kblock_clocks(W) + (wide ? epilogue_clocks(W) : 0.0));
+  if (rest > 0) c += kblocks * kblock_clocks(W / f) + (wide ? epilogue_clocks(W / f) : 0.0);
+  if (!wide) c = c * 1.05 + epilogue_clocks(W / f);
+  return c;
+}
+// One CTA per 128 x 256 tile, double-buffered accumulator: the same clocks per k-block and SM.
+static double single_clocks(int m, int n, int kblocks, int sms) {
+  const int tiles = ((m + 255) / 256) * ((n + 127) / 128);
+  const int rounds = (tiles + sms - 1) / sms;
+  return rounds * kblocks * kblock_clocks(256) * 1.05 + epilogue_clocks(256);
+}
+
+// W = 0: not a problem for the pair kernels.  Switch TC_WIDE: 0 = only the 256 x 256 kernel, >= 64 = that width.
+static PairPlan pair_plan(int m, int n, int kblocks, int sms) {
+  PairPlan best = {0, 0.0, false};
+  if (m < 512 || n < 512 || sms < 2) return best;
+  const int forced = opt(OPT_TC_WIDE);
+  if (forced >= 64) {
+    int W = forced > tc::W_MAX ? tc::W_MAX : forced / 32 * 32;
+    return PairPlan{W, pair_clocks(m, n, kblocks, W, true, sms), true};
+  }
+  best = PairPlan{256, pair_clocks(m, n, kblocks, 256, false, sms), false};
+  if (forced != 0)
+    for (int W = tc::W_MAX; W >= 320; W -= 64) {
+      const double c = pair_clocks(m, n, kblocks, W, true, sms);
+      if (c < best.clocks) best = PairPlan{W, c, true};
+    }
+  if (single_clocks(m, n, kblocks, sms) < best.clocks) return PairPlan{0, 0.0, false};
+  return best;
+}
+
 // Blackwell tile selection (takes the place of the reference's tuned per-architecture tables,
 // src/e5m2effma_tuned.h): tiles of 256 rows x 128 columns when they fill the machine or m is large,
 // else 128 x 128.  Operand pairs: FP8 x FP8 -> kind::f8f6f4; BF16 x BF16 -> kind::f16; FP8 x BF16 in
@@ -337,15 +393,12 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   // widened FP8 operand of a mixed pair is written in that layout too); the CTA-pair kernel takes K-contiguous ones only
   const int kind = f8 ? 0 : 1;
   const int ft = conv == 1 ? a_dtype : (conv == 2 ? b_dtype : E5MA_E5M2);
-  // CTA pairs (gemm_tc2.cuh) for big unmixed problems: 256 x 256 tiles, half the operand bytes per CTA
+  // CTA pairs (gemm_tc2.cuh, gemm_tc3.cuh) for unmixed problems with both operands K-contiguous: the plan with the
+  // lowest estimated time wins (pair_plan below); the one-CTA kernel stays for everything else.
   const bool use_pair = opt(OPT_TC_PAIR) != 0;   // experiments: 0 keeps every problem on single CTAs
-  if (use_pair && a_kc && b_kc && conv == 0 && m >= 512 && n >= 512 && ((m + 255) / 256) * ((n + 255) / 256) >= sms / 2) {
-    CUtensorMap pi, pj, pi2, pi4;
-    if (!make_map(&pi, A, elem_bytes(a_dtype), k, m, lda, 128, false) ||
-        !make_map(&pj, B, elem_bytes(b_dtype), k, n, ldb, 128, false) ||
-        !make_map(&pi2, A, elem_bytes(a_dtype), k, m, lda, 64, false) ||
-        !make_map(&pi4, A, elem_bytes(a_dtype), k, m, lda, 32, false))
-      return cudaErrorNotSupported;
+  const int kblocks = (k * (f8 ? 1 : 2) + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
+  const PairPlan plan = use_pair && a_kc && b_kc && conv == 0 ? pair_plan(m, n, kblocks, sms) : PairPlan{0, 0.0, false};
+  if (plan.W > 0) {
     const int fi2 = f8 ? (a_dtype == E5MA_E5M2 ? 1 : 0) : 1, fj2 = f8 ? (b_dtype == E5MA_E5M2 ? 1 : 0) : 1;
     const auto vec_ok2 = [](const void *p, int ld, int dtype) {
       return ((uintptr_t)p & 15u) == 0 && ((size_t)ld * elem_bytes(dtype)) % 16 == 0;
@@ -356,6 +409,31 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
     if (o.c && !((o.c_dtype == E5MA_FP32 || o.c_dtype == E5MA_BF16) && vec_ok2(o.c, o.ldc, o.c_dtype))) pm.vec = 0;
     if (o.bias && !((o.bias_dtype == E5MA_FP32 || o.bias_dtype == E5MA_BF16) && ((uintptr_t)o.bias & 15u) == 0)) pm.vec = 0;
     if (o.sa_vec && ((uintptr_t)o.sa & 15u)) pm.vec = 0;
+    if (plan.wide) {
+      const int W = plan.W;
+      const int tiles = ((m + W - 1) / W) * ((n + P_TILE - 1) / P_TILE);
+      int pairs = sms / 2;
+      if (tiles < pairs) pairs = tiles;
+      const WidePlan wp = wide_plan(W, tiles, pairs);
+      CUtensorMap wi[3], wj;
+      // boxes of W / 4 rows for whole tiles; W / 8 and W / 16 only when the last round is sliced (they must be
+      // multiples of the 8-row swizzle group; unused maps repeat the first)
+      if (!make_map(&wj, B, elem_bytes(b_dtype), k, n, ldb, 128, false) ||
+          !make_map(&wi[0], A, elem_bytes(a_dtype), k, m, lda, W / 4, false) ||
+          !make_map(&wi[1], A, elem_bytes(a_dtype), k, m, lda, wp.slices >= 2 ? W / 8 : W / 4, false) ||
+          !make_map(&wi[2], A, elem_bytes(a_dtype), k, m, lda, wp.slices == 4 ? W / 16 : W / 4, false))
+        return cudaErrorNotSupported;
+      const WideDescs wd = {{instr_desc(fj2, fi2, 256, W / 2), instr_desc(fj2, fi2, 256, wp.slices >= 2 ? W / 4 : W / 2),
+                             instr_desc(fj2, fi2, 256, wp.slices == 4 ? W / 8 : W / 2)}};
+      return f8 ? launch_pairw<0>(wi, wj, m, n, k * 1, wp, wd, o, pm, pairs, s)
+                : launch_pairw<1>(wi, wj, m, n, k * 2, wp, wd, o, pm, pairs, s);
+    }
+    CUtensorMap pi, pj, pi2, pi4;
+    if (!make_map(&pi, A, elem_bytes(a_dtype), k, m, lda, 128, false) ||
+        !make_map(&pj, B, elem_bytes(b_dtype), k, n, ldb, 128, false) ||
+        !make_map(&pi2, A, elem_bytes(a_dtype), k, m, lda, 64, false) ||
+        !make_map(&pi4, A, elem_bytes(a_dtype), k, m, lda, 32, false))
+      return cudaErrorNotSupported;
     const uint32_t pdesc = instr_desc(fj2, fi2, 256, 256);
     const PairSplit ps = {instr_desc(fj2, fi2, 256, 128), instr_desc(fj2, fi2, 256, 64)};
     return f8 ? launch_pair<0>(pi, pj, pi2, pi4, m, n, k * 1, pdesc, ps, o, pm, sms, s)
@@ -410,5 +488,6 @@ extern "C" unsigned int e5b_gemm_fault(void) {
   if (cudaDeviceSynchronize() != cudaSuccess) return 0xFFFFFFFFu;
   if (cudaMemcpyFromSymbol(&v, e5b::tc::g_fault, sizeof v) != cudaSuccess) return 0xFFFFFFFFu;
   cudaMemcpyToSymbol(e5b::tc::g_fault, &zero, sizeof zero);
-  return v;
+  const unsigned int gv = e5b::gemv_fault_read_and_clear();   // the persistent GEMV's waits are bounded the same way
+  return v ? v : (gv ? (gv | 0x80000000u) : 0u);
 }

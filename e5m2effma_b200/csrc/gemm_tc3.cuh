@@ -124,7 +124,7 @@ gemm_tc_pairw_kernel(const __grid_constant__ CUtensorMap map_i0, const __grid_co
       for (int t = pair; t < items && ok; t += pairs, ++lt) {
         int i0, j0, w, level;
         item_at(t, i0, j0, w, level);
-        const uint32_t idesc_t = wd.idesc[level];
+        const uint32_t idesc_t = level == 0 ? wd.idesc[0] : (level == 1 ? wd.idesc[1] : wd.idesc[2]);
         const uint32_t box_step = ((uint32_t)(w / 4) * STAGE_K_BYTES) >> 4;   // second box, in descriptor address units
         if (!mbar_wait(acc_empty, (lt & 1u) ^ 1u, abort_flag, (2u << 24) | 0xFFFFu)) { ok = false; break; }
         tc_fence_after();

@@ -261,6 +261,288 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_async_kernel(const uint8_t
   if (o.amax) block_amax(o.amax, mx);
 }
 
+// ---- persistent kernel with a bulk-copy weight ring ------------------------------------------------
+// One CTA per SM walks over 16-row tiles of W.  A producer warp streams the tile's rows into a ring of
+// shared-memory stages with bulk asynchronous copies (16 rows x 1 KiB per stage, one copy per row, completion
+// counted on an mbarrier), several stages ahead and across tile boundaries, so the bytes in flight cost neither
+// registers nor issue slots of the eight consumer warps.  The consumers split a stage's 1 KiB of K between them
+// (128 bytes per warp, as in the kernels above) and feed mma.sync.m16n8k16 with X as the 8-column operand.
+//
+// What makes the instruction stream short: X is staged once per CTA in shared memory as FP16, W is widened
+// to FP16 with one byte permute (E5M2 is the upper byte of an FP16) or one converter instruction (E4M3) per two
+// codes, and the FP16 tensor-core path is used -- products stay exact (4 x 11 significant bits), sums are FP32.
+// FP8 X always converts exactly.  A BF16 X does whenever every value is representable in FP16, which the CTA
+// checks while staging; if one is not (|x| >= 65520, or bits below 2^-24), the CTA stages X as BF16 instead and
+// widens W to BF16 as the kernels above do.  Both paths add the same exact products in the same order, so the
+// choice does not show in the result.
+//
+// Rows are padded to 1088 bytes in the ring and X columns to a pitch of 16 mod 128 bytes: the 16-byte reads of
+// a quarter warp (two rows / columns x four k-chunks) then hit distinct banks.
+// Per tile the eight partial 16 x 8 tiles meet in shared memory in a fixed order (two buffers alternate, one
+// named barrier per tile) and 128 threads run the common epilogue.  Every mbarrier wait is bounded.
+constexpr int GB_ROW_PITCH = 1024 + 64;
+constexpr int GB_STAGE_BYTES = 16 * GB_ROW_PITCH;
+constexpr int GB_MAX_STAGES = 8;
+constexpr int GB_THREADS = GV_WARPS * 32 + 32;
+constexpr unsigned long long GB_WAIT_LIMIT = 4000000000ull;
+
+__device__ unsigned int g_gemv_fault;
+
+__device__ __forceinline__ uint32_t gb_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool gb_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool gb_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned int who) {
+  if (gb_try(bar, parity)) return true;
+  const unsigned long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (gb_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((unsigned long long)(clock64() - t0) > GB_WAIT_LIMIT) {
+      *abort_flag = 1;
+      atomicCAS(&g_gemv_fault, 0u, who);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void gb_bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_f16_16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// four FP8 codes (ascending k) -> FP16 pairs (k0,k1), (k2,k3), exact
+template <int T>
+__device__ __forceinline__ void fp8x4_to_f16x2(uint32_t w, uint32_t &lo, uint32_t &hi) {
+  if (T == E5MA_E5M2) { lo = __byte_perm(w, 0, 0x1404); hi = __byte_perm(w, 0, 0x3424); }
+  else { lo = e4m3x2_to_f16x2(w); hi = e4m3x2_to_f16x2(w >> 16); }
+}
+
+template <int AT, int XT>
+__global__ void __launch_bounds__(GB_THREADS, 1) gemv_bulk_kernel(const uint8_t *__restrict__ W, int lda,
+                                                                  const uint8_t *__restrict__ X, int ldx, int m, int n,
+                                                                  int k, int stages, int x_pitch, OutDesc o) {
+  extern __shared__ __align__(128) uint8_t gb_raw[];
+  // [x: n columns x x_pitch bytes][ring: stages x 16 rows x 1088 bytes][red: 2 x 8 x 16 x 9 floats][barriers][flags]
+  uint8_t *xs = gb_raw;
+  uint8_t *ringp = xs + (size_t)n * x_pitch;
+  float (*red)[GV_WARPS][16][9] = reinterpret_cast<float (*)[GV_WARPS][16][9]>(ringp + (size_t)stages * GB_STAGE_BYTES);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(red) + 2 * GV_WARPS * 16 * 9 * sizeof(float));
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * GB_MAX_STAGES);
+  volatile int *x_fits_f16 = abort_flag + 1;
+  const uint32_t bar0 = gb_smem(bars), ring_s = gb_smem(ringp);
+  const auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  const auto empty_bar = [&](int s) { return bar0 + 8u * (GB_MAX_STAGES + s); };
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int tiles = (m + 15) / 16, chunks = (k + 1023) / 1024;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full_bar(s)), "r"(1));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty_bar(s)), "r"(GV_WARPS));
+    }
+    *abort_flag = 0;
+    *x_fits_f16 = 1;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  float mx = 0.f;
+  if (warp == GV_WARPS) {
+    // ---------------- producer: one bulk copy per row and stage, issued by lanes 0..15 ----------------
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      const int row = tile * 16 + lane;
+      const bool live = lane < 16 && row < m;
+      const int live_rows = m - tile * 16 < 16 ? m - tile * 16 : 16;
+      const uint8_t *src = W + (size_t)(live ? row : 0) * lda;
+      for (int c = 0; c < chunks; ++c) {
+        const uint32_t bytes = (uint32_t)(k - c * 1024 < 1024 ? k - c * 1024 : 1024);
+        ok = gb_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)c);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        if (lane == 0)
+          asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }"
+                       ::"r"(full_bar(s)), "r"(bytes * (uint32_t)live_rows) : "memory");
+        __syncwarp();
+        if (live) gb_bulk_load(ring_s + (uint32_t)s * GB_STAGE_BYTES + (uint32_t)lane * GB_ROW_PITCH, src + (size_t)c * 1024, bytes, full_bar(s));
+        if (++s == stages) { s = 0; ph ^= 1u; }
+      }
+    }
+  } else {
+    // ---------------- consumers ----------------
+    // X -> shared memory, FP16 when every value converts exactly (FP8 always does), else BF16 as it is
+    const int ct = threadIdx.x;                       // 0 .. 255
+    constexpr int XE = XT == E5MA_BF16 ? 8 : 16;      // elements per 16-byte load
+    const int per_col = k / XE;                       // k is a multiple of 16
+    bool fits = true;
+    for (int idx = ct; idx < n * per_col; idx += GV_WARPS * 32) {
+      const int j = idx / per_col, q = idx - j * per_col;
+      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(X + ((size_t)j * ldx + (size_t)q * XE) * (XT == E5MA_BF16 ? 2 : 1)));
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      if (XT == E5MA_BF16) {
+        uint32_t h[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xFFFF0000u);
+          const __half2 hh = __floats2half2_rn(lo, hi);
+          const float2 back = __half22float2(hh);
+          fits = fits && back.x == lo && back.y == hi;
+          h[e] = *reinterpret_cast<const uint32_t *>(&hh);
+        }
+        *reinterpret_cast<uint4 *>(xs + (size_t)j * x_pitch + (size_t)q * 16) = make_uint4(h[0], h[1], h[2], h[3]);
+      } else {
+        uint32_t h[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) fp8x4_to_f16x2<XT == E5MA_BF16 ? E5MA_E5M2 : XT>(w[e], h[2 * e], h[2 * e + 1]);
+        uint4 *dst = reinterpret_cast<uint4 *>(xs + (size_t)j * x_pitch + (size_t)q * 32);
+        dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+        dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+      }
+    }
+    if (!fits) *x_fits_f16 = 0;
+    asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
+    const bool f16 = *x_fits_f16 != 0;
+    if (XT == E5MA_BF16 && !f16) {
+      asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");   // everybody has read the flag and is done with the FP16 copy
+      for (int idx = ct; idx < n * per_col; idx += GV_WARPS * 32) {
+        const int j = idx / per_col, q = idx - j * per_col;
+        *reinterpret_cast<uint4 *>(xs + (size_t)j * x_pitch + (size_t)q * 16) =
+            __ldg(reinterpret_cast<const uint4 *>(X + ((size_t)j * ldx + (size_t)q * 8) * 2));
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
+    }
+
+    const OutScalars r = out_begin(o);
+    const uint8_t *xcol = xs + (size_t)g * x_pitch;
+    const bool xlive = g < n;
+    int s = 0;
+    uint32_t ph = 0, lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++lt) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int c = 0; c < chunks; ++c) {
+        ok = gb_wait(full_bar(s), ph, abort_flag, (2u << 24) | (uint32_t)c);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        const uint8_t *stage = ringp + (size_t)s * GB_STAGE_BYTES;
+        const int kw = c * 1024 + warp * 128;            // first k of this warp's slice
+        if (kw < k) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int kk = kw + h * 64 + t * 16;
+            const bool live = kk < k;
+            uint4 qa = make_uint4(0, 0, 0, 0), qb = qa, x0 = qa, x1 = qa;
+            if (live) {
+              qa = *reinterpret_cast<const uint4 *>(stage + g * GB_ROW_PITCH + (kk - c * 1024));
+              qb = *reinterpret_cast<const uint4 *>(stage + (g + 8) * GB_ROW_PITCH + (kk - c * 1024));
+              if (xlive) {
+                x0 = *reinterpret_cast<const uint4 *>(xcol + (size_t)kk * 2);
+                x1 = *reinterpret_cast<const uint4 *>(xcol + (size_t)kk * 2 + 16);
+              }
+            }
+            const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
+            const uint32_t xw[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            if (f16) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                uint32_t a0, a2, a1, a3;
+                fp8x4_to_f16x2<AT>(wa[e], a0, a2);
+                fp8x4_to_f16x2<AT>(wb[e], a1, a3);
+                mma_f16_16816((e & 1) ? acc2 : acc, a0, a1, a2, a3, xw[2 * e], xw[2 * e + 1]);
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                uint32_t a0, a2, a1, a3;
+                fp8x4_to_bf16x2<AT>(wa[e], a0, a2);
+                fp8x4_to_bf16x2<AT>(wb[e], a1, a3);
+                mma_bf16_16816((e & 1) ? acc2 : acc, a0, a1, a2, a3, xw[2 * e], xw[2 * e + 1]);
+              }
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(empty_bar(s)) : "memory");
+        if (++s == stages) { s = 0; ph ^= 1u; }
+      }
+      if (!ok) break;
+      // the eight partial tiles meet in a fixed order; buffers alternate so that the next tile's partials do not
+      // overwrite what the 128 reducing threads of this tile may still be reading
+      const int buf = lt & 1;
+      red[buf][warp][g][2 * t] = __fadd_rn(acc[0], acc2[0]);
+      red[buf][warp][g][2 * t + 1] = __fadd_rn(acc[1], acc2[1]);
+      red[buf][warp][g + 8][2 * t] = __fadd_rn(acc[2], acc2[2]);
+      red[buf][warp][g + 8][2 * t + 1] = __fadd_rn(acc[3], acc2[3]);
+      asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
+      if (threadIdx.x < 128) {
+        const int il = threadIdx.x & 15, j = threadIdx.x >> 4, i = tile * 16 + il;
+        if (i < m && j < n) {
+          float sum = red[buf][0][il][j];
+#pragma unroll
+          for (int w = 1; w < GV_WARPS; ++w) sum = __fadd_rn(sum, red[buf][w][il][j]);
+          mx = fmaxf(mx, out_store(o, r, i, j, sum));
+        }
+      }
+    }
+  }
+  if (o.amax) block_amax(o.amax, mx);
+  else __syncthreads();
+}
+
+// Shared memory of the persistent kernel for a given problem, and the stage count that fits (0: does not fit).
+struct BulkPlan { int stages, x_pitch, smem; };
+static BulkPlan gemv_bulk_plan(int n, int k) {
+  BulkPlan p;
+  p.x_pitch = (k * 2 + 127) / 128 * 128 + 16;
+  const int fixed = n * p.x_pitch + 2 * GV_WARPS * 16 * 9 * 4 + 2 * GB_MAX_STAGES * 8 + 64;
+  p.stages = (232448 - 1024 - fixed) / GB_STAGE_BYTES;
+  if (p.stages > GB_MAX_STAGES) p.stages = GB_MAX_STAGES;
+  if (p.stages < 3) p.stages = 0;
+  p.smem = fixed + p.stages * GB_STAGE_BYTES;
+  return p;
+}
+
+template <int AT>
+static cudaError_t gemv_bulk_x(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
+                               const OutDesc &o, int sms, const BulkPlan &p, cudaStream_t s) {
+  const int tiles = (m + 15) / 16;
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+#define E5B_GEMV_BULK(XT)                                                                                     \
+  {                                                                                                           \
+    static SmemOptIn optin;                                                                                   \
+    if (const cudaError_t e = optin.ensure(gemv_bulk_kernel<AT, XT>, 232448 - 1024)) return e;                \
+    gemv_bulk_kernel<AT, XT><<<grid, GB_THREADS, p.smem, s>>>(A, lda, X, ldx, m, n, k, p.stages, p.x_pitch, o); \
+  }
+  switch (x_dtype) {
+    case E5MA_BF16: E5B_GEMV_BULK(E5MA_BF16) break;
+    case E5MA_E5M2: E5B_GEMV_BULK(E5MA_E5M2) break;
+    case E5MA_E4M3: E5B_GEMV_BULK(E5MA_E4M3) break;
+    default: return cudaErrorNotSupported;
+  }
+#undef E5B_GEMV_BULK
+  return cudaGetLastError();
+}
+
+unsigned int gemv_fault_read_and_clear() {
+  unsigned int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemv_fault, sizeof v) != cudaSuccess) return 0xFFFFFFFFu;
+  cudaMemcpyToSymbol(g_gemv_fault, &zero, sizeof zero);
+  return v;
+}
+
 template <int AT, int GA_STAGES>
 static cudaError_t gemv_async_x(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
                                 const OutDesc &o, cudaStream_t s) {
@@ -313,7 +595,18 @@ cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda,
   // Measured on B200 (8192 x 8192 weights, batch 1 / 8): the cp.async pipeline with X prefetched one step
   // ahead takes 15.2 / 15.8 us, the register-load kernel 15.8 / 16.6 us.  the GEMV_KERNEL switch = 0
   // (experiments) selects the latter.
-  const bool use_async = opt(OPT_GEMV_KERNEL) != 0;
+  // Persistent bulk-copy kernel: only on request (switch GEMV_KERNEL = 2) and when X fits beside a ring of at
+  // least three stages.  Measured on B200 (8192 x 8192 weights): 24 us against 15.6 us for the cp.async kernel --
+  // bulk copies keep too few bytes in flight per SM, whatever their size.
+  const int which = opt(OPT_GEMV_KERNEL);
+  const BulkPlan bp = gemv_bulk_plan(n, k);
+  if (bp.stages && which == 2) {
+    note_route(ROUTE_GEMV_PERSISTENT);
+    if (a_dtype == E5MA_E5M2) return gemv_bulk_x<E5MA_E5M2>(x_dtype, A, lda, X, ldx, m, n, k, o, sms, bp, s);
+    if (a_dtype == E5MA_E4M3) return gemv_bulk_x<E5MA_E4M3>(x_dtype, A, lda, X, ldx, m, n, k, o, sms, bp, s);
+    return cudaErrorNotSupported;
+  }
+  const bool use_async = which != 0;
   note_route(ROUTE_GEMV);
   if (use_async) {
     int stages = 2;   // 32 KiB per block: every row tile of an 8192-row matrix is resident in one wave

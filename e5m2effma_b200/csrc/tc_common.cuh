@@ -242,7 +242,9 @@ __device__ __forceinline__ float drain32(const OutDesc &o, const OutScalars &r, 
     }
 #pragma unroll
     for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fabsf(acc[e]));
-    store32<DT>((uint8_t *)o.d + ((size_t)j * o.ldd + ib) * elem_bytes(DT), acc, r.qs);
+    const size_t off = ((size_t)j * o.ldd + ib) * elem_bytes(DT);
+    store32<DT>((uint8_t *)o.d + off, acc, r.qs);
+    for (int p = 0; p < o.npeers; ++p) store32<DT>((uint8_t *)o.peer[p] + off, acc, r.qs);
   } else {
 #pragma unroll
     for (int e = 0; e < 32; ++e) {   // fully unrolled: acc[] stays in registers
@@ -255,6 +257,7 @@ __device__ __forceinline__ float drain32(const OutDesc &o, const OutScalars &r, 
         if (o.c) v = __fmaf_rn(o.beta, load_elem(o.c_dtype, o.c, (size_t)j * o.ldc + i, r.csinv), v);
         mx = fmaxf(mx, fabsf(v));
         store_out<DT>(o.d, (size_t)j * o.ldd + i, v, r.qs);
+        for (int p = 0; p < o.npeers; ++p) store_out<DT>(o.peer[p], (size_t)j * o.ldd + i, v, r.qs);
       }
     }
   }
@@ -304,6 +307,7 @@ __device__ __forceinline__ float drain32_t(const OutDesc &o, const OutScalars &r
     if (jb + e < n) {
       mx = fmaxf(mx, fabsf(acc[e]));
       store_out<DT>(o.d, (size_t)(jb + e) * o.ldd + i, acc[e], r.qs);
+      for (int p = 0; p < o.npeers; ++p) store_out<DT>(o.peer[p], (size_t)(jb + e) * o.ldd + i, acc[e], r.qs);
     }
   }
   return mx;

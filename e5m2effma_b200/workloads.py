@@ -8,11 +8,23 @@ scale_inv = 1 / scale.  Every workload exposes
     units               algorithmic FLOPs (GEMM) or bytes (GEMV / AdamW / cast) of one pass
     host_inputs() / device_inputs / result   the buffers an end-to-end step has to move
 """
-import math
-
 import torch
 
-from . import capi
+
+class _Codes:
+    """dtype and enum codes of include/e5m2effma.h; kept here so that building a workload's input data does not
+    load the library (the CPU reference arm of the benchmark generates the same inputs without it)."""
+    E4M3, BF16, FP16, FP32, E5M2 = 0, 1, 2, 3, 4
+    OP_N, OP_T = 0, 1
+    OK = 0
+    SCALING_OUTER = 1
+
+    def __getattr__(self, name):          # everything else (calls, structures) comes from the real binding
+        from . import capi as real
+        return getattr(real, name)
+
+
+capi = _Codes()
 
 FP8_MAX = {capi.E5M2: 57344.0, capi.E4M3: 448.0}
 TORCH_DT = {capi.E4M3: torch.float8_e4m3fn, capi.E5M2: torch.float8_e5m2, capi.BF16: torch.bfloat16,
@@ -30,8 +42,13 @@ def _gen(seed, dev):
     return g
 
 
+QUANTIZER = None   # None: e5ma_cast on the GPU.  The reference arm of the benchmark installs a CPU encoder here.
+
+
 def quantize(x32, dtype, scale=None):
-    """FP32 CUDA tensor -> uint8 codes of `dtype` = encode(x * scale), via e5ma_cast."""
+    """FP32 tensor -> uint8 codes of `dtype` = encode(x * scale), via e5ma_cast (or the installed QUANTIZER)."""
+    if QUANTIZER is not None:
+        return QUANTIZER(x32, dtype, scale)
     out = torch.empty(x32.shape, dtype=torch.uint8, device=x32.device)
     s = None
     if scale is not None:
@@ -159,6 +176,14 @@ class AdamWorkload:
                                                     self.amax.data_ptr())
         _check(capi.adam(self.cfg, self.count, P, G, M, V, Q, stream), "e5ma_adam")
 
+    def launch_range(self, stream, i0, i1):
+        """The same step over elements [i0, i1) only (one rank's chunk of a sharded parameter set)."""
+        P, G = capi.tensor(self.p.data_ptr() + 2 * i0, capi.BF16), capi.tensor(self.g.data_ptr() + 2 * i0, capi.BF16)
+        M, V = capi.tensor(self.m.data_ptr() + 2 * i0, capi.BF16), capi.tensor(self.v.data_ptr() + 2 * i0, capi.BF16)
+        Q = None if self.q is None else capi.tensor(self.q.data_ptr() + i0, capi.E4M3, None, self.qscale.data_ptr(),
+                                                    self.amax.data_ptr())
+        _check(capi.adam(self.cfg, i1 - i0, P, G, M, V, Q, stream), "e5ma_adam")
+
     launches_per_pass = 1
 
     def io_tensors(self):
@@ -189,6 +214,12 @@ class CastWorkload:
         S = capi.tensor(self.src.data_ptr(), self.src_dtype, self.scale.data_ptr())
         D = capi.tensor(self.dst.data_ptr(), self.dst_dtype, None, self.scale.data_ptr(), self.amax.data_ptr())
         _check(capi.cast(S, D, self.count, stream), "e5ma_cast")
+
+    def launch_range(self, stream, i0, i1):
+        es = {capi.FP32: 4, capi.BF16: 2, capi.FP16: 2, capi.E4M3: 1, capi.E5M2: 1}
+        S = capi.tensor(self.src.data_ptr() + i0 * es[self.src_dtype], self.src_dtype, self.scale.data_ptr())
+        D = capi.tensor(self.dst.data_ptr() + i0 * es[self.dst_dtype], self.dst_dtype, None, self.scale.data_ptr(), self.amax.data_ptr())
+        _check(capi.cast(S, D, i1 - i0, stream), "e5ma_cast")
 
     launches_per_pass = 1
 

@@ -34,6 +34,22 @@ int e5b_set_option(const char *name, int value);
  * No counterpart in the reference (one GEMM kernel, one GEMV kernel). */
 int e5b_last_route(void);
 
+/* e5ma_gemm (same arguments, same checks in the same order, same kernels) whose epilogue stores every
+ * output element not only to D but also, at the same element offset, to num_peers (0..7) further
+ * buffers peer_d[0..num_peers-1]: the other GPUs' copies of this call's block of D, mapped into the
+ * current device's address space (CUDA IPC handles or peer access; each must have D's alignment
+ * modulo 16 bytes and D's leading dimension).  This is the all-gather of a column- or row-sharded
+ * output fused into the GEMM / GEMV that produces it: the stores travel over NVLink while the tensor
+ * cores work on the next tile, no collective is launched and nothing is read from a peer.  amax is
+ * reduced into this GPU's D->amax only.  The peers may read their copy once they know this call has
+ * completed (an event, or any later collective on the same streams, e.g. the amax max-all-reduce).
+ * peer_d is host memory, read during the call only.
+ * No counterpart in the reference, which is a single-device library. */
+e5ma_status e5b_gemm_bcast(e5ma_op transa, e5ma_op transb, int m, int n, int k, float alpha,
+                           const e5ma_tensor *A, int lda, const e5ma_tensor *B, int ldb, float beta,
+                           const e5ma_tensor *C, int ldc, const e5ma_tensor *D, int ldd,
+                           const e5ma_tensor *bias, int num_peers, void *const *peer_d, cudaStream_t stream);
+
 /* One Adam / AdamW step (the arithmetic of e5ma_adam, same cfg) over a list of num_tensors tensors in as
  * few launches as possible: up to 24 tensors share a launch, each block of the grid works on one
  * 16384-element chunk of one tensor.  counts[t] is the element count of tensor t; params, grads, exp_avgs,

@@ -16,7 +16,7 @@ def test_matmul_argument_checks_and_no_cpu_path():
         F.matmul(torch.zeros(16, dtype=torch.bfloat16), torch.zeros(16, 16, dtype=torch.bfloat16))
     with pytest.raises(TypeError, match="float8_e5m2, float8_e4m3fn, bfloat16 or float32"):
         F.matmul(torch.zeros(16, 16, dtype=torch.float16), torch.zeros(16, 16, dtype=torch.bfloat16))
-    with pytest.raises(ValueError, match="a must be a CUDA tensor"):
+    with pytest.raises(ValueError, match="CUDA tensor is required"):
         F.matmul(fp8((16, 16)), fp8((16, 16), torch.float8_e4m3fn))
 
 

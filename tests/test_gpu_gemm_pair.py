@@ -109,6 +109,21 @@ def test_same_data_without_tail_slices_and_on_single_ctas(case):
     assert _run(case, TC_PAIR=0) in (capi.ROUTE_TC_256, capi.ROUTE_TC_128)
 
 
+WIDE_EXTRA = [GemmCase(1, 0, 3584, 3584, 272, E5M2, E4M3, E5M2, -1, BF16, 1.0, 0.0, vec=1, seed=901, tight=True),   # W = 512: 98 tiles, 24 left -> 2 slices
+              GemmCase(1, 0, 4864, 3840, 144, E4M3, E4M3, BF16, -1, -1, 1.25, 1.0, vec=2, seed=902),                  # W = 512: 150 tiles, 2 left -> 4 slices
+              GemmCase(1, 0, 8192, 512, 400, E5M2, E5M2, FP32, BF16, FP32, 1.0, 0.5, vec=3, seed=903, tight=True),    # a column shard: n = 512
+              GemmCase(1, 0, 2500, 2100, 528, BF16, BF16, FP16, -1, -1, 1.0, 0.0, seed=904)]
+
+
+@pytest.mark.parametrize("width", [512, 480, 384, 224])
+@pytest.mark.parametrize("case", CASES[::4] + WIDE_EXTRA, ids=lambda c: c.label())
+def test_wide_tiles_within_tolerance(case, width):
+    """The wide-tile pair kernel at forced tile widths: full-width accumulators (512), a width whose half is not a
+    multiple of the epilogue's 32-row step (480), widths with sliced last rounds, narrow tiles for column shards."""
+    from e5m2effma_b200 import capi
+    assert _run(case, TC_WIDE=width) == capi.ROUTE_TC_PAIR_WIDE
+
+
 def test_pair_kernel_is_deterministic():
     from e5m2effma_b200 import capi
     d = GemmData(GemmCase(1, 0, 2321, 2309, 784, E5M2, E4M3, BF16, -1, BF16, 1.0, 0.0, vec=1, seed=77))
