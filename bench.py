@@ -365,24 +365,39 @@ class Timing:
             ms = float(t.item())
         return ms
 
-    def run(self, step, steps, warmup, graph, sampler=None):
+    def run(self, step, steps, warmup, graph, sampler=None, graph_optional=False):
         """step(i, stream_ptr).  graph=True: the K steps are captured once into a CUDA graph and replayed (so that
         microsecond-scale kernels are not timed behind the Python launch path); steps with NCCL calls run on the stream."""
         torch, stream = self.torch, self.stream
+        # W warm-up steps, and more of them until about 10 ms of GPU work have run: after an idle spell the SM clock
+        # needs milliseconds to come back up, which a handful of microsecond-scale launches would not cover
+        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0.record(stream)
         for i in range(warmup):
             step(i, stream.cuda_stream)
+        w1.record(stream)
+        self.barrier()
+        per = self.max_over_ranks(w0.elapsed_time(w1)) / max(warmup, 1)
+        for i in range(min(2000, int(10.0 / max(per, 1e-3)) - warmup)):
+            step(warmup + i, stream.cuda_stream)
         self.barrier()
         g = None
         if graph:
-            cs = torch.cuda.Stream()
-            cs.wait_stream(stream)
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(cs):
-                with torch.cuda.graph(g, stream=cs):
-                    for i in range(steps):
-                        step(i, cs.cuda_stream)
-            g.replay()
+            try:
+                cs = torch.cuda.Stream()
+                cs.wait_stream(stream)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(cs):
+                    with torch.cuda.graph(g, stream=cs):
+                        for i in range(steps):
+                            step(i, cs.cuda_stream)
+                g.replay()
+            except Exception:
+                if not graph_optional:
+                    raise
+                g = None
             self.barrier()
+        self.timed_as = "cuda_graph" if g is not None else "stream"
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         if g is not None:
@@ -578,15 +593,20 @@ def measure_sharded(name, w, rot, tm, world, rank, dev, steps, warmup, sampler, 
     out["kernel_only"] = {"ms_per_step": k_ms, "strong_efficiency": t1_ms / (world * k_ms)}
     has_coll = sh.needs_gather or sh.amax is not None
     best = k_ms
+    # steps of a few microseconds would be timed behind the Python launch path of the collective: replay them from a
+    # CUDA graph (NCCL calls capture); long steps run on the stream as before
+    graph_collectives = os.environ.get("E5MA_BENCH_GRAPH_COLLECTIVES", "auto") != "0" and k_ms < 0.2
     if has_coll:
-        n_ms = tm.run(sh.step_nccl, steps, warmup, graph=False, sampler=sampler)
-        out["with_collectives_nccl"] = {"ms_per_step": n_ms, "strong_efficiency": t1_ms / (world * n_ms),
+        n_ms = tm.run(sh.step_nccl, steps, warmup, graph=graph_collectives, sampler=sampler, graph_optional=True)
+        nccl_timed_as = tm.timed_as
+        out["with_collectives_nccl"] = {"ms_per_step": n_ms, "strong_efficiency": t1_ms / (world * n_ms), "timed_as": nccl_timed_as,
                                         "collectives": ("NCCL all-gather of the output (%d bytes)" % sh.gather_bytes if sh.needs_gather else "")
                                         + (" + max-all-reduce of amax" if sh.amax is not None else "")}
         best = n_ms
         if sh.peerbuf is not None:
-            f_ms = tm.run(sh.step_fused, steps, warmup, graph=False, sampler=sampler)
-            out["with_collectives_fused"] = {"ms_per_step": f_ms, "strong_efficiency": t1_ms / (world * f_ms),
+            f_ms = tm.run(sh.step_fused, steps, warmup, graph=graph_collectives, sampler=sampler, graph_optional=True)
+            fused_timed_as = tm.timed_as
+            out["with_collectives_fused"] = {"ms_per_step": f_ms, "strong_efficiency": t1_ms / (world * f_ms), "timed_as": fused_timed_as,
                                              "collectives": "output blocks stored into every peer's D by the epilogue (e5b_gemm_bcast) + "
                                              + ("max-all-reduce of amax" if sh.amax is not None else "one-float all-reduce as completion barrier")}
             best = min(best, f_ms)

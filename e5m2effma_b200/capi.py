@@ -53,6 +53,8 @@ def _load():
     lib.e5b_gemm_bcast.argtypes = lib.e5ma_gemm.argtypes[:-1] + [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
     lib.e5b_set_option.restype = ctypes.c_int
     lib.e5b_set_option.argtypes = [ctypes.c_char_p, ctypes.c_int]
+    lib.e5b_tuned_plan.restype = ctypes.c_int
+    lib.e5b_tuned_plan.argtypes = [ctypes.c_int] * 4
     lib.e5b_last_route.restype = ctypes.c_int
     lib.e5b_last_route.argtypes = []
     lib.e5b_adam_multi.restype = ctypes.c_int
@@ -86,6 +88,11 @@ def set_option(name, value):
     the library's own choice."""
     if lib.e5b_set_option(name.encode(), -1 if value is None else int(value)) != 0:
         raise KeyError(f"unknown option {name}")
+
+
+def tuned_plan(elem_bytes, m, n, k):
+    """Tuned-table plan of a GEMM problem (-2: no entry); see e5b_tuned_plan."""
+    return int(lib.e5b_tuned_plan(elem_bytes, m, n, k))
 
 
 def last_route():

@@ -233,9 +233,16 @@ enum Opt {
   OPT_GEMV_U,         // E5MA_GEMV_U        k-steps in flight per warp of the register-load kernel
   OPT_GEMV_MT,        // E5MA_GEMV_MT       2: 32 rows per block in the register-load kernel
   OPT_MIXED_PAIR,     // E5MA_MIXED_PAIR    0: FP8 x BF16 problems never take the CTA-pair kernel
+  OPT_GEMV_KMAP,      // E5MA_GEMV_KMAP     1: each warp of the cp.async GEMV walks a contiguous eighth of K
   OPT_COUNT
 };
 int opt(Opt which);
+
+// Measured plan for a GEMM problem: the table named by E5MA_TUNE_FILE (read once), then the compiled-in table of
+// tuned_sm100.h.  TUNED_NONE when neither has the problem.  GEMV settings likewise (key: 0 kernel, 1 stages, 2 kmap).
+constexpr int TUNED_NONE = -1000000;
+int tuned_gemm_plan(int elem_bytes, int m, int n, int k);
+int tuned_gemv(int key);
 
 // Which kernel the last e5ma_gemm call of this host thread launched (e5b_last_route()).
 enum Route { ROUTE_NONE = 0, ROUTE_GEMV = 1, ROUTE_GEMV_PERSISTENT = 2, ROUTE_TC_PAIR = 3, ROUTE_TC_PAIR_WIDE = 4,

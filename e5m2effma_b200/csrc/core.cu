@@ -12,6 +12,8 @@
 #include <stdlib.h>
 #include <string.h>
 #include "common.cuh"
+#include "tuned_sm100.h"
+#include <vector>
 
 namespace e5b {
 
@@ -35,7 +37,7 @@ e5ma_status cuda_fail(cudaError_t e, const char *what) {
 // ---- switches and the route record ----------------------------------------------------------------
 static std::atomic<int> g_opt[OPT_COUNT];
 static const char *const kOptNames[OPT_COUNT] = {"FORCE_SIMT", "TC_PAIR", "TC_SPLIT", "TC_GRID", "TC_WIDE", "GEMV_KERNEL",
-                                                 "GEMV_STAGES", "GEMV_U", "GEMV_MT", "MIXED_PAIR"};
+                                                 "GEMV_STAGES", "GEMV_U", "GEMV_MT", "MIXED_PAIR", "GEMV_KMAP"};
 static void opt_init() {
   static std::once_flag once;
   std::call_once(once, [] {
@@ -53,6 +55,50 @@ static void opt_init() {
 int opt(Opt which) {
   opt_init();
   return g_opt[which].load(std::memory_order_relaxed);
+}
+
+// ---- tuned tables ---------------------------------------------------------------------------------
+struct TunedGemm { int eb, m, n, k, plan; };
+static const TunedGemm kTunedGemm[] = {E5B_TUNED_GEMM {0, 0, 0, 0, 0}};
+struct TunedFile { std::vector<TunedGemm> gemm; int gemv[3] = {TUNED_NONE, TUNED_NONE, TUNED_NONE}; };
+
+// Text table: one entry per line, `gemm <elem bytes> <m> <n> <k> <plan>` or `gemv kernel|stages|kmap <value>`;
+// anything else (comments, blank lines) is skipped.
+static const TunedFile &tuned_file() {
+  static TunedFile tf;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char *path = getenv("E5MA_TUNE_FILE");
+    FILE *f = path && path[0] ? fopen(path, "r") : nullptr;
+    if (!f) return;
+    char line[256];
+    while (fgets(line, sizeof line, f)) {
+      TunedGemm g;
+      char key[32];
+      int v;
+      if (sscanf(line, "gemm %d %d %d %d %d", &g.eb, &g.m, &g.n, &g.k, &g.plan) == 5) tf.gemm.push_back(g);
+      else if (sscanf(line, "gemv %31s %d", key, &v) == 2) {
+        if (!strcmp(key, "kernel")) tf.gemv[0] = v;
+        else if (!strcmp(key, "stages")) tf.gemv[1] = v;
+        else if (!strcmp(key, "kmap")) tf.gemv[2] = v;
+      }
+    }
+    fclose(f);
+  });
+  return tf;
+}
+int tuned_gemm_plan(int elem_bytes, int m, int n, int k) {
+  for (const TunedGemm &g : tuned_file().gemm)
+    if (g.eb == elem_bytes && g.m == m && g.n == n && g.k == k) return g.plan;
+  for (const TunedGemm &g : kTunedGemm)
+    if (g.eb == elem_bytes && g.m == m && g.n == n && g.k == k && g.eb != 0) return g.plan;
+  return TUNED_NONE;
+}
+int tuned_gemv(int key) {
+  if (key < 0 || key > 2) return TUNED_NONE;
+  if (tuned_file().gemv[key] != TUNED_NONE) return tuned_file().gemv[key];
+  const int compiled[3] = {E5B_TUNED_GEMV_KERNEL, E5B_TUNED_GEMV_STAGES, E5B_TUNED_GEMV_KMAP};
+  return compiled[key];
 }
 
 static thread_local int t_route = ROUTE_NONE;
@@ -287,6 +333,11 @@ extern "C" int e5b_set_option(const char *name, int value) {
 }
 
 extern "C" int e5b_last_route(void) { return e5b::t_route; }
+
+extern "C" int e5b_tuned_plan(int elem_bytes, int m, int n, int k) {
+  const int p = e5b::tuned_gemm_plan(elem_bytes, m, n, k);
+  return p == e5b::TUNED_NONE ? -2 : p;
+}
 
 extern "C" const char *e5ma_status_string(e5ma_status s) {
   switch (s) {

@@ -258,6 +258,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty(buf));
+      if (!md.transposed) {   // e5b_gemm_bcast: this warp's block of the tile goes to the peers (the transposed epilogue stores to them directly)
+        const int rb = i0 + half * (BI / 2), re_ = i0 + (half + 1) * (BI / 2);
+        const int rend = re_ < i0 + rows ? re_ : i0 + rows;
+        bcast_block<DT>(o, j0 + quad * 32, n, rb, rend < m ? rend : m);
+      }
     }
     if (o.amax) {
       mx = warp_max(mx);
@@ -359,10 +364,17 @@ static double single_clocks(int m, int n, int kblocks, int sms) {
 }
 
 // W = 0: not a problem for the pair kernels.  Switch TC_WIDE: 0 = only the 256 x 256 kernel, >= 64 = that width.
-static PairPlan pair_plan(int m, int n, int kblocks, int sms) {
+// Without a switch, a measured entry of the tuned table decides before the model.
+static PairPlan pair_plan(int m, int n, int k, int elem_bytes, int kblocks, int sms) {
   PairPlan best = {0, 0.0, false};
   if (m < 512 || n < 512 || sms < 2) return best;
   const int forced = opt(OPT_TC_WIDE);
+  if (forced < 0) {
+    const int plan = tuned_gemm_plan(elem_bytes, m, n, k);
+    if (plan == -1) return best;
+    if (plan == 0) return PairPlan{256, pair_clocks(m, n, kblocks, 256, false, sms), false};
+    if (plan >= 64 && plan <= tc::W_MAX && plan % 32 == 0) return PairPlan{plan, pair_clocks(m, n, kblocks, plan, true, sms), true};
+  }
   if (forced >= 64) {
     int W = forced > tc::W_MAX ? tc::W_MAX : forced / 32 * 32;
     return PairPlan{W, pair_clocks(m, n, kblocks, W, true, sms), true};
@@ -397,7 +409,7 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   // lowest estimated time wins (pair_plan below); the one-CTA kernel stays for everything else.
   const bool use_pair = opt(OPT_TC_PAIR) != 0;   // experiments: 0 keeps every problem on single CTAs
   const int kblocks = (k * (f8 ? 1 : 2) + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
-  const PairPlan plan = use_pair && a_kc && b_kc && conv == 0 ? pair_plan(m, n, kblocks, sms) : PairPlan{0, 0.0, false};
+  const PairPlan plan = use_pair && a_kc && b_kc && conv == 0 ? pair_plan(m, n, k, f8 ? 1 : 2, kblocks, sms) : PairPlan{0, 0.0, false};
   if (plan.W > 0) {
     const int fi2 = f8 ? (a_dtype == E5MA_E5M2 ? 1 : 0) : 1, fj2 = f8 ? (b_dtype == E5MA_E5M2 ? 1 : 0) : 1;
     const auto vec_ok2 = [](const void *p, int ld, int dtype) {

@@ -140,6 +140,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
   cluster_sync_all();          // both CTAs' barriers are initialised before anyone signals the other
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t peer_abort = map_to_rank(smem_u32(const_cast<int *>(abort_flag)), rank ^ 1u);   // the other CTA's abort flag
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -161,7 +162,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
           const int kb = backwards ? kblocks - 1 - kq : kq;
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1u;
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)kb)) { ok = false; break; }
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)kb, peer_abort)) { ok = false; break; }
           const uint32_t lead_full = map_to_rank(full_bar(s), 0);
           if (rank == 0) mbar_expect_tx(full_bar(s), pair_bytes);   // both CTAs' bytes land on this barrier
           const uint32_t sj = ring + s * P_STAGE_BYTES, si = sj + P_HALF_BYTES;
@@ -181,13 +182,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
         item_at(t, i0, j0, cols);
         const uint32_t idesc_t = cols == P_TILE ? idesc : (cols == P_TILE / 2 ? ps.idesc2 : ps.idesc4);
         const uint32_t buf = lt & 1u, use = lt >> 1;
-        if (!mbar_wait(acc_empty(buf), (use & 1u) ^ 1u, abort_flag, (2u << 24) | 0xFFFFu)) { ok = false; break; }
+        if (!mbar_wait(acc_empty(buf), (use & 1u) ^ 1u, abort_flag, (2u << 24) | 0xFFFFu, peer_abort)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * P_TILE;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1u;
-          if (!mbar_wait(full_bar(s), ph, abort_flag, (2u << 24) | (uint32_t)kb)) { ok = false; break; }
+          if (!mbar_wait(full_bar(s), ph, abort_flag, (2u << 24) | (uint32_t)kb, peer_abort)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sj = ring + s * P_STAGE_BYTES, si = sj + P_HALF_BYTES;
           const uint64_t dj = kmajor_sw128_desc(sj), di = kmajor_sw128_desc(si);
@@ -217,7 +218,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
       item_at(t, i0, j0, cols);
       j0 += (int)rank * 128;
       const uint32_t buf = lt & 1u, use = lt >> 1;
-      ok = mbar_wait(acc_full(buf), use & 1u, abort_flag, (3u << 24) | (uint32_t)warp);
+      ok = mbar_wait(acc_full(buf), use & 1u, abort_flag, (3u << 24) | (uint32_t)warp, peer_abort);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -234,6 +235,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_rank(acc_empty(buf), 0));
+      // e5b_gemm_bcast: this warp's block of the tile goes to the peers while the MMA warp is already filling the buffer again
+      const int rb = i0 + half * (P_TILE / 2), re_ = i0 + (half + 1) * (P_TILE / 2);
+      const int rend = re_ < i0 + cols ? re_ : i0 + cols;
+      bcast_block<DT>(o, j0 + quad * 32, n, rb, rend < m ? rend : m);
     }
     if (o.amax) {
       mx = warp_max(mx);

@@ -1,17 +1,17 @@
 // Tensor-core GEMM on CTA pairs with wide tiles: 256 columns j x W rows i per pair, W up to 512.
 //
-// Why wider than the 256 x 256 tiles of gemm_tc2.cuh: with every SM loading its operand halves from L2 the
-// mainloop of that kernel is bound by the L2-to-SM path, not by the tensor pipe -- a 256 x 256 x 128-byte
-// k-block moves 32 KiB per CTA and takes about 710 clocks where its MMAs need 512 (the same ~46 bytes per
-// clock and SM also explains the one-CTA mixed kernel).  A 256 x W tile moves (128 + W / 2) * 128 bytes per
-// CTA for 2 W clocks of MMA work: at W = 512 that is 48 KiB for 1024 clocks, 25 % fewer bytes per FLOP, and
-// loads and MMAs are about balanced.
+// What wider tiles buy: a 256 x W tile moves (128 + W / 2) * 128 operand bytes per CTA and k-block for 2 W clocks
+// of MMA work -- at W = 512 that is 25 % fewer bytes per FLOP than the 256 x 256 tiles of gemm_tc2.cuh (measured:
+// L2 throughput 30 % instead of 43 %, DRAM 13 % instead of 16 %) -- and half as many tiles.  What they do not buy on
+// B200 is a faster mainloop: the FP8 mainloop is power-bound there (under ncu this kernel runs at a higher SM clock
+// with a proportionally less busy tensor pipe; clock x pipe-active is the same for both kernels), so the gain is
+// the 2 to 7 % that fewer bytes and fewer tile transitions are worth on long-K problems.
 //
 // Price: the two W / 2-column accumulators (one N = W / 2 MMA each per 32 bytes of K) fill the 512 columns
 // of tensor memory, so there is no second buffer and the epilogue of a tile is not hidden behind the next
 // tile's mainloop (the TMA ring keeps filling meanwhile).  That pays when K is long next to the epilogue;
 // the launcher chooses between this kernel, its width, and the double-buffered 256 x 256 kernel from a
-// small cost model.
+// tuned table and a small cost model.
 //
 // Roles, barriers, bounded waits, pairing and the common exit are those of gemm_tc2.cuh.  No load is
 // multicast: each CTA fetches its own 128 rows of op(B)^T and its own two boxes of W / 4 rows of op(A).
@@ -85,6 +85,7 @@ gemm_tc_pairw_kernel(const __grid_constant__ CUtensorMap map_i0, const __grid_co
   cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t peer_abort = map_to_rank(smem_u32(const_cast<int *>(abort_flag)), rank ^ 1u);   // the other CTA's abort flag
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -103,7 +104,7 @@ gemm_tc_pairw_kernel(const __grid_constant__ CUtensorMap map_i0, const __grid_co
         const bool backwards = ((t / pairs) & 1) != 0;
         for (int kq = 0; kq < kblocks; ++kq) {
           const int kb = backwards ? kblocks - 1 - kq : kq;
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)kb)) { ok = false; break; }
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)kb, peer_abort)) { ok = false; break; }
           const uint32_t lead_full = map_to_rank(full_bar(s), 0);
           if (rank == 0) mbar_expect_tx(full_bar(s), pair_bytes);
           const uint32_t sj = ring + s * stage_bytes, si = sj + P_HALF_BYTES;
@@ -126,10 +127,10 @@ gemm_tc_pairw_kernel(const __grid_constant__ CUtensorMap map_i0, const __grid_co
         item_at(t, i0, j0, w, level);
         const uint32_t idesc_t = level == 0 ? wd.idesc[0] : (level == 1 ? wd.idesc[1] : wd.idesc[2]);
         const uint32_t box_step = ((uint32_t)(w / 4) * STAGE_K_BYTES) >> 4;   // second box, in descriptor address units
-        if (!mbar_wait(acc_empty, (lt & 1u) ^ 1u, abort_flag, (2u << 24) | 0xFFFFu)) { ok = false; break; }
+        if (!mbar_wait(acc_empty, (lt & 1u) ^ 1u, abort_flag, (2u << 24) | 0xFFFFu, peer_abort)) { ok = false; break; }
         tc_fence_after();
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (!mbar_wait(full_bar(s), ph, abort_flag, (2u << 24) | (uint32_t)kb)) { ok = false; break; }
+          if (!mbar_wait(full_bar(s), ph, abort_flag, (2u << 24) | (uint32_t)kb, peer_abort)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sj = ring + s * stage_bytes, si = sj + P_HALF_BYTES;
           const uint64_t dj = kmajor_sw128_desc(sj), di = kmajor_sw128_desc(si);
@@ -160,7 +161,7 @@ gemm_tc_pairw_kernel(const __grid_constant__ CUtensorMap map_i0, const __grid_co
     for (int t = pair; t < items && ok; t += pairs, ++lt) {
       int i0, j0, w, level;
       item_at(t, i0, j0, w, level);
-      ok = mbar_wait(acc_full, lt & 1u, abort_flag, (3u << 24) | (uint32_t)warp);
+      ok = mbar_wait(acc_full, lt & 1u, abort_flag, (3u << 24) | (uint32_t)warp, peer_abort);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -179,6 +180,7 @@ gemm_tc_pairw_kernel(const __grid_constant__ CUtensorMap map_i0, const __grid_co
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_rank(acc_empty, 0));
+      bcast_block<DT>(o, j0 + (int)rank * 128 + quad * 32, n, ibase, lim);   // e5b_gemm_bcast: this warp's block goes to the peers
     }
     if (o.amax) {
       mx = warp_max(mx);

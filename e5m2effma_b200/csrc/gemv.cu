@@ -147,17 +147,21 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_mma_kernel(const uint8_t *
 // what it copied itself.  Out-of-range rows and k positions are copied with a source size of 0,
 // which zero-fills the slot.
 
-__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, bool live) {
+// wide: ask L2 to fetch the whole 256-byte pair of lines on a miss (the warp's next k-step is the other half)
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void *gsrc, bool live, bool wide) {
   const int bytes = live ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(bytes) : "memory");
+  if (wide) asm volatile("cp.async.cg.shared.global.L2::256B [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(bytes) : "memory");
+  else asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// kmap 0: the eight warps interleave 128-byte k-steps (step it of warp w is k-block w + 8 it); kmap 1: each warp
+// owns one contiguous eighth of K and walks it 128 bytes at a time (its consecutive steps are neighbours in DRAM).
 template <int AT, int XT, int GA_STAGES>
 __global__ void __launch_bounds__(GV_WARPS * 32) gemv_async_kernel(const uint8_t *__restrict__ W, int lda,
                                                                    const uint8_t *__restrict__ X, int ldx, int m, int n,
-                                                                   int k, OutDesc o) {
+                                                                   int k, int kmap, OutDesc o) {
   extern __shared__ __align__(16) uint8_t ring_raw[];        // [warp][stage][fragment 0..3][lane] x 16 bytes
   __shared__ float red[GV_WARPS][16][9];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -170,16 +174,20 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_async_kernel(const uint8_t
   const int ra = row0 + g, rb = ra + 8;
   const bool la = ra < m, lb = rb < m;
   const uint8_t *wa = W + (size_t)(la ? ra : 0) * lda, *wb = W + (size_t)(lb ? rb : 0) * lda;
-  // this warp's k-steps: 128 bytes at kc = (warp + 8 * it) * 128
-  const int steps = k > warp * 128 ? (k - warp * 128 + GV_WARPS * 128 - 1) / (GV_WARPS * 128) : 0;
+  // this warp's k-steps of 128 bytes: step it starts at kstart(it)
+  const int kblocks = (k + 127) / 128, per_warp = (kblocks + GV_WARPS - 1) / GV_WARPS;
+  const int steps = kmap ? (kblocks - warp * per_warp < per_warp ? (kblocks > warp * per_warp ? kblocks - warp * per_warp : 0) : per_warp)
+                         : (k > warp * 128 ? (k - warp * 128 + GV_WARPS * 128 - 1) / (GV_WARPS * 128) : 0);
+  const auto kstart = [&](int it) { return (kmap ? warp * per_warp + it : warp + GV_WARPS * it) * 128; };
+  const bool wide = kmap != 0;
   const auto issue = [&](int it) {
     if (it < steps) {
-      const int kc = (warp + GV_WARPS * it) * 128 + t * 16;
+      const int kc = kstart(it) + t * 16;
       const uint32_t dst = my_ring_s + (uint32_t)(it % GA_STAGES) * 2048;
-      cp_async16(dst, wa + kc, la && kc < k);
-      cp_async16(dst + 512, wb + kc, lb && kc < k);
-      cp_async16(dst + 1024, wa + kc + 64, la && kc + 64 < k);
-      cp_async16(dst + 1536, wb + kc + 64, lb && kc + 64 < k);
+      cp_async16(dst, wa + kc, la && kc < k, wide);
+      cp_async16(dst + 512, wb + kc, lb && kc < k, wide);
+      cp_async16(dst + 1024, wa + kc + 64, la && kc + 64 < k, wide);
+      cp_async16(dst + 1536, wb + kc + 64, lb && kc + 64 < k, wide);
     }
     cp_async_commit();     // one group per step, also when it is empty: the wait below counts groups
   };
@@ -191,7 +199,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_async_kernel(const uint8_t
   const uint8_t *xcol = X + (size_t)g * ldx * XB;
   const bool xlive = g < n;
   const auto load_x = [&](int it, uint4 (&xq)[2][XW]) {
-    const int kc = (warp + GV_WARPS * it) * 128;
+    const int kc = kstart(it);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int kk = kc + h * 64 + t * 16;
@@ -548,11 +556,12 @@ static cudaError_t gemv_async_x(int x_dtype, const uint8_t *A, int lda, const ui
                                 const OutDesc &o, cudaStream_t s) {
   constexpr int GA_SMEM = GV_WARPS * GA_STAGES * 2048;
   const unsigned grid = (unsigned)((m + 15) / 16);
+  const int kmap = (opt(OPT_GEMV_KMAP) >= 0 ? opt(OPT_GEMV_KMAP) : tuned_gemv(2)) > 0 ? 1 : 0;
 #define E5B_GEMV_CASE(XT, slot_)                                                                                            \
   {                                                                                                                         \
     static SmemOptIn optin;                                                                                                 \
     if (const cudaError_t e = optin.ensure(gemv_async_kernel<AT, XT, GA_STAGES>, GA_SMEM)) return e;                        \
-    gemv_async_kernel<AT, XT, GA_STAGES><<<grid, GV_WARPS * 32, GA_SMEM, s>>>(A, lda, X, ldx, m, n, k, o);                             \
+    gemv_async_kernel<AT, XT, GA_STAGES><<<grid, GV_WARPS * 32, GA_SMEM, s>>>(A, lda, X, ldx, m, n, k, kmap, o);                       \
   }
   switch (x_dtype) {
     case E5MA_BF16: E5B_GEMV_CASE(E5MA_BF16, 0) break;
@@ -598,7 +607,7 @@ cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda,
   // Persistent bulk-copy kernel: only on request (switch GEMV_KERNEL = 2) and when X fits beside a ring of at
   // least three stages.  Measured on B200 (8192 x 8192 weights): 24 us against 15.6 us for the cp.async kernel --
   // bulk copies keep too few bytes in flight per SM, whatever their size.
-  const int which = opt(OPT_GEMV_KERNEL);
+  const int which = opt(OPT_GEMV_KERNEL) >= 0 ? opt(OPT_GEMV_KERNEL) : tuned_gemv(0);
   const BulkPlan bp = gemv_bulk_plan(n, k);
   if (bp.stages && which == 2) {
     note_route(ROUTE_GEMV_PERSISTENT);
@@ -609,7 +618,7 @@ cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda,
   const bool use_async = which != 0;
   note_route(ROUTE_GEMV);
   if (use_async) {
-    int stages = 2;   // 32 KiB per block: every row tile of an 8192-row matrix is resident in one wave
+    int stages = tuned_gemv(1);   // 2 = 32 KiB per block: every row tile of an 8192-row matrix is resident in one wave
     if (opt(OPT_GEMV_STAGES) > 0) stages = opt(OPT_GEMV_STAGES);
     if (a_dtype == E5MA_E5M2)
       return stages == 2 ? gemv_async_x<E5MA_E5M2, 2>(x_dtype, A, lda, X, ldx, m, n, k, o, s)

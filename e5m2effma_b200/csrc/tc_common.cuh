@@ -37,8 +37,11 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the limit ran out or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned int who) {
+// Bounded wait: false when the limit ran out or another role already aborted.  peer_abort: cluster address of the
+// abort flag of the other CTA of a pair (0: none) -- raised together with the local one, so that the peer leaves at
+// its next poll instead of waiting out its own limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned int who,
+                                          uint32_t peer_abort = 0) {
   if (mbar_try(bar, parity)) return true;
   const unsigned long long t0 = clock64();
   for (;;) {
@@ -47,6 +50,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (*abort_flag) return false;
     if ((unsigned long long)(clock64() - t0) > WAIT_LIMIT) {
       *abort_flag = 1;
+      if (peer_abort) asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer_abort), "r"(1u) : "memory");
       atomicCAS(&g_fault, 0u, who);
       return false;
     }
@@ -242,9 +246,7 @@ __device__ __forceinline__ float drain32(const OutDesc &o, const OutScalars &r, 
     }
 #pragma unroll
     for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fabsf(acc[e]));
-    const size_t off = ((size_t)j * o.ldd + ib) * elem_bytes(DT);
-    store32<DT>((uint8_t *)o.d + off, acc, r.qs);
-    for (int p = 0; p < o.npeers; ++p) store32<DT>((uint8_t *)o.peer[p] + off, acc, r.qs);
+    store32<DT>((uint8_t *)o.d + ((size_t)j * o.ldd + ib) * elem_bytes(DT), acc, r.qs);
   } else {
 #pragma unroll
     for (int e = 0; e < 32; ++e) {   // fully unrolled: acc[] stays in registers
@@ -257,11 +259,46 @@ __device__ __forceinline__ float drain32(const OutDesc &o, const OutScalars &r, 
         if (o.c) v = __fmaf_rn(o.beta, load_elem(o.c_dtype, o.c, (size_t)j * o.ldc + i, r.csinv), v);
         mx = fmaxf(mx, fabsf(v));
         store_out<DT>(o.d, (size_t)j * o.ldd + i, v, r.qs);
-        for (int p = 0; p < o.npeers; ++p) store_out<DT>(o.peer[p], (size_t)j * o.ldd + i, v, r.qs);
       }
     }
   }
   return mx;
+}
+
+// e5b_gemm_bcast, column-per-lane epilogues: after a warp has drained its part of a tile into the local D -- rows
+// [r0, r1) of the 32 columns starting at c0 -- it copies that block to every peer's D.  A lane's own stores are
+// 32 to 128 bytes per column, 32 columns apart in memory; sent over NVLink like that they would travel as
+// small, scattered writes (measured: the GEMM ran at half speed).  Copied back out of L2 instead, consecutive
+// lanes take consecutive 16-byte pieces of one column, so every remote store instruction writes runs of up to
+// 512 contiguous bytes.  Only this warp's own stores are read, so a warp-level barrier orders them.
+template <int DT>
+__device__ __forceinline__ void bcast_block(const OutDesc &o, int c0, int n, int r0, int r1) {
+  if (o.npeers == 0 || r1 <= r0) return;
+  __syncwarp();
+  constexpr int ES = elem_bytes(DT);
+  const int lane = threadIdx.x & 31;
+  const int cols = n - c0 < 32 ? n - c0 : 32;
+  if (cols <= 0) return;
+  const size_t col_bytes = (size_t)o.ldd * ES;
+  const uint8_t *src = (const uint8_t *)o.d + ((size_t)c0 * o.ldd + r0) * ES;
+  const int run = (r1 - r0) * ES;                       // bytes per column
+  const bool aligned = ((((uintptr_t)src) | col_bytes) & 15u) == 0;
+  const int chunks = aligned ? run >> 4 : 0;            // whole 16-byte pieces per column
+  for (int idx = lane; idx < cols * chunks; idx += 32) {
+    const int c = idx / chunks, q = idx - c * chunks;
+    const size_t off = (size_t)c * col_bytes + ((size_t)q << 4);
+    const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(src + off));
+    const size_t doff = (size_t)(src - (const uint8_t *)o.d) + off;
+    for (int p = 0; p < o.npeers; ++p) *reinterpret_cast<uint4 *>((uint8_t *)o.peer[p] + doff) = v;
+  }
+  const int rest0 = chunks << 4;                        // bytes of each column not covered above
+  for (int idx = lane; idx < cols * (run - rest0); idx += 32) {
+    const int c = idx / (run - rest0), b = rest0 + idx - c * (run - rest0);
+    const size_t off = (size_t)c * col_bytes + b;
+    const uint8_t v = __ldcg(src + off);
+    const size_t doff = (size_t)(src - (const uint8_t *)o.d) + off;
+    for (int p = 0; p < o.npeers; ++p) ((uint8_t *)o.peer[p])[doff] = v;
+  }
 }
 
 // The same for a kernel that ran with swapped operand roles: the thread's TMEM lane is row i, its 32

@@ -26,6 +26,14 @@ unsigned int e5b_gemm_fault(void);
  * Takes the place of rebuilding the reference with another tuned table (src/e5m2effma_tuned.h). */
 int e5b_set_option(const char *name, int value);
 
+/* The tuned table's plan for a GEMM with operands of elem_bytes (1: FP8 pair, 2: BF16 pair) and this shape:
+ * -1 one-CTA kernel, 0 the 256 x 256 CTA-pair kernel, W >= 64 the wide-tile pair kernel with 256 x W tiles;
+ * -2 when the table has no entry (the built-in cost model then plans the problem).  The table is the one
+ * compiled in (csrc/tuned_sm100.h, written by `python -m e5m2effma_b200.tune --header`), overridden entry by
+ * entry by the text file named in E5MA_TUNE_FILE (written by `python -m e5m2effma_b200.tune --write FILE`,
+ * read once per process).  Counterpart of the reference's generated src/e5m2effma_tuned.h. */
+int e5b_tuned_plan(int elem_bytes, int m, int n, int k);
+
 /* Which kernel the last e5ma_gemm call of the calling host thread launched: 0 none (rejected, or
  * m == 0 / n == 0), 1 streaming GEMV, 2 persistent GEMV, 3 CTA-pair tensor-core GEMM (256 x 256
  * tiles), 4 the same with wide tiles (256 x up to 512), 5 / 6 one-CTA tensor-core GEMM with
