@@ -42,6 +42,7 @@
 #include "tc_common.cuh"
 #include "gemm_tc2.cuh"
 #include "gemm_tc3.cuh"
+#include "gemm_tc4.cuh"
 
 namespace e5b {
 namespace tc {
@@ -106,8 +107,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     j0 = tj * BM;
   };
 
+  if (threadIdx.x == 32) { prefetch_map(&map_i); prefetch_map(&map_j); prefetch_map(&map_ih); }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); mbar_init(ready_bar(s), EPI_WARPS); }
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); mbar_init(ready_bar(s), EPI_WARPS / md.wgroups); }
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -213,9 +215,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
       item_at(t, i0, j0, rows);
       if (CONV != 0) {
         // Mixed pairs: these warps first widen the FP8 operand of every k-block of the tile (widen_block), then
-        // drain the accumulator.
-        const int ct = threadIdx.x - 64;
+        // drain the accumulator.  The eight warps work as WG groups that take k-blocks in turn: one pass over a
+        // k-block (wait, read, convert, write, fence, arrive) is a chain of dependent latencies of several hundred
+        // clocks, and with all eight warps on the same k-block that chain, not the tensor pipe, set the pace of
+        // the mainloop; groups overlap WG such chains.
+        const int WG = md.wgroups, GT = 32 * EPI_WARPS / WG;
+        const int ct = threadIdx.x - 64, grp = ct / GT, cg = ct - grp * GT;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          if ((int)(it % (uint32_t)WG) != grp) continue;        // warp-uniform: the group is a whole number of warps
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1u;
           ok = mbar_wait(full_bar(s), ph, abort_flag, (5u << 24) | (uint32_t)kb);
@@ -224,8 +231,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
           uint8_t *stage = smem_raw + (ring - smem_u32(smem_raw)) + s * C::STAGE_BYTES;
           const uint8_t *raw = stage + C::J_BYTES + C::I_BYTES;
           uint8_t *dst = stage + (CONV == 1 ? C::J_BYTES : 0);
-          if (CONV == 2 && md.mn_m) widen_block<FT, true>(raw, dst, ct);
-          else widen_block<FT, false>(raw, dst, ct);
+          const bool mn = CONV == 2 && md.mn_m;
+          if (WG == 4) { if (mn) widen_block<FT, true, 64>(raw, dst, cg); else widen_block<FT, false, 64>(raw, dst, cg); }
+          else if (WG == 2) { if (mn) widen_block<FT, true, 128>(raw, dst, cg); else widen_block<FT, false, 128>(raw, dst, cg); }
+          else { if (mn) widen_block<FT, true, 256>(raw, dst, cg); else widen_block<FT, false, 256>(raw, dst, cg); }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
           __syncwarp();
           if (lane == 0) mbar_arrive(ready_bar(s));
@@ -451,6 +460,39 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
     return f8 ? launch_pair<0>(pi, pj, pi2, pi4, m, n, k * 1, pdesc, ps, o, pm, sms, s)
               : launch_pair<1>(pi, pj, pi2, pi4, m, n, k * 2, pdesc, ps, o, pm, sms, s);
   }
+  // Mixed FP8 x BF16 pairs with both operands K-contiguous and enough 256 x 256 tiles to keep at least half of the
+  // SM pairs busy can take the CTA-pair kernel of gemm_tc4.cuh (FP8 operand on the M side, so an FP8 A runs
+  // transposed) -- only on request (switch MIXED_PAIR): it measures slower than the one-CTA kernel below.
+  if (conv != 0 && a_kc && b_kc && opt(OPT_MIXED_PAIR) > 0 && k >= 512) {
+    const bool trp = conv == 1;
+    const uint8_t *pf = trp ? A : B, *pb = trp ? B : A;
+    const int ldf = trp ? lda : ldb, ldbf = trp ? ldb : lda;
+    const int ef = trp ? m : n, eb = trp ? n : m;                // extents along the M side (FP8) / N side (BF16)
+    const int tiles = ((ef + P_TILE - 1) / P_TILE) * ((eb + P_TILE - 1) / P_TILE);
+    if (ef >= 256 && eb >= 256 && (tiles >= sms / 4 || opt(OPT_MIXED_PAIR) == 2)) {
+      CUtensorMap mb[3];
+      if (!make_map(&mb[0], pb, 2, k, eb, ldbf, 128, false) ||
+          !make_map(&mb[1], pb, 2, k, eb, ldbf, 64, false) || !make_map(&mb[2], pb, 2, k, eb, ldbf, 32, false))
+        return cudaErrorNotSupported;
+      const auto vec_okx = [](const void *p, int ld, int dtype) {
+        return ((uintptr_t)p & 15u) == 0 && ((size_t)ld * elem_bytes(dtype)) % 16 == 0;
+      };
+      EpiMode xm = {};
+      xm.transposed = trp ? 1 : 0;
+      xm.split = opt(OPT_TC_SPLIT) != 0;
+      xm.vec = vec_okx(o.d, o.ldd, o.d_dtype);
+      if (o.c && !((o.c_dtype == E5MA_FP32 || o.c_dtype == E5MA_BF16) && vec_okx(o.c, o.ldc, o.c_dtype))) xm.vec = 0;
+      if (o.bias && !((o.bias_dtype == E5MA_FP32 || o.bias_dtype == E5MA_BF16) && ((uintptr_t)o.bias & 15u) == 0)) xm.vec = 0;
+      if (o.sa_vec && ((uintptr_t)o.sa & 15u)) xm.vec = 0;
+      const uint32_t xdesc = instr_desc(1, 1, 256, 256);
+      const PairSplit xs = {instr_desc(1, 1, 256, 128), instr_desc(1, 1, 256, 64)};
+      const int fdt = trp ? a_dtype : b_dtype;
+      if (trp) return fdt == E5MA_E5M2 ? launch_mixpair_dt<E5MA_E5M2, true>(pf, ldf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s)
+                                       : launch_mixpair_dt<E5MA_E4M3, true>(pf, ldf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s);
+      return fdt == E5MA_E5M2 ? launch_mixpair_dt<E5MA_E5M2, false>(pf, ldf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s)
+                              : launch_mixpair_dt<E5MA_E4M3, false>(pf, ldf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s);
+    }
+  }
   // Mixed pairs widen their FP8 operand in shared memory; that costs least when the FP8 operand sits on the
   // MMA's M side (128 rows per tile instead of 256).  The M side is op(B)^T, so an FP8 A is handled by
   // running the kernel on the transposed problem (operands and m / n swapped, transposed epilogue).
@@ -461,7 +503,9 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   const int en = tr ? n : m, em = tr ? m : n;                  // N-side / M-side extents
   const int kconv = conv ? 2 : 0;                              // after the swap the FP8 operand is always on the M side
   const int tiles256 = ((en + 255) / 256) * ((em + BM - 1) / BM);
-  const bool wide = en > 128 && (tiles256 >= sms || en % 256 == 0 || en > 1024);
+  const int tiles128 = ((en + 127) / 128) * ((em + BM - 1) / BM);
+  const bool underfilled = tiles256 < sms && tiles128 > tiles256 && tiles256 * 4 < sms * 3;   // 256-row tiles would idle a quarter of the SMs
+  const bool wide = en > 128 && !underfilled && (tiles256 >= sms || en % 256 == 0 || en > 1024);
   const int bi = wide ? 256 : 128;
   CUtensorMap mi, mj, mih;   // mih: the N-side operand with half-height boxes, for the half tiles of the last round
   const bool n_kc = tr ? b_kc : a_kc, m_kc = tr ? a_kc : b_kc;   // storage of the N-side / M-side operand
@@ -482,6 +526,7 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   md.mn_n = n_kc ? 0 : 1;
   md.mn_m = m_kc ? 0 : 1;
   md.split = wide && opt(OPT_TC_SPLIT) != 0;
+  md.wgroups = opt(OPT_WIDEN_GROUPS) == 1 || opt(OPT_WIDEN_GROUPS) == 2 || opt(OPT_WIDEN_GROUPS) == 4 ? opt(OPT_WIDEN_GROUPS) : 2;   // measured on B200: 2 groups
   md.vec = vec_ok(o.d, o.ldd, o.d_dtype);
   if (o.c && !((o.c_dtype == E5MA_FP32 || o.c_dtype == E5MA_BF16) && vec_ok(o.c, o.ldc, o.c_dtype))) md.vec = 0;
   if (o.bias && !((o.bias_dtype == E5MA_FP32 || o.bias_dtype == E5MA_BF16) && ((uintptr_t)o.bias & 15u) == 0)) md.vec = 0;

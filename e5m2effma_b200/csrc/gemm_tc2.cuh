@@ -124,6 +124,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_cons
     j0 = tj * P_TILE;
   };
 
+  if (threadIdx.x == 32) { prefetch_map(&map_i); prefetch_map(&map_j); prefetch_map(&map_i2); prefetch_map(&map_i4); }
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 2 * EPI_WARPS); }

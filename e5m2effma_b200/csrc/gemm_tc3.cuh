@@ -68,6 +68,7 @@ gemm_tc_pairw_kernel(const __grid_constant__ CUtensorMap map_i0, const __grid_co
     j0 = tj * P_TILE;
   };
 
+  if (threadIdx.x == 32) { prefetch_map(&map_i0); prefetch_map(&map_j); prefetch_map(&map_i1); prefetch_map(&map_i2); }
   if (threadIdx.x == 0) {
     for (int s = 0; s < 8; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     mbar_init(acc_full, 1);

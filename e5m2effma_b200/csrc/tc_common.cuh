@@ -62,6 +62,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
                ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
 
+// fetch a tensor map (a kernel parameter) into the descriptor cache before the first copy needs it
+__device__ __forceinline__ void prefetch_map(const CUtensorMap *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
 }
@@ -208,9 +213,10 @@ __device__ __forceinline__ void store32(void *p, const float v[32], float qs) {
 // What the epilogue of one launch needs beyond OutDesc: whether D (and C) admit 16-byte vector
 // access (base and leading dimension multiples of 16 bytes) and whether bias / C have a dtype the
 // vector path reads directly.
+// wgroups: into how many groups the epilogue warps split to widen alternate k-blocks of a mixed problem (1, 2, 4).
 // split: the last partial wave of tiles is cut into half tiles.  transposed: the kernel was given the
 // operands in swapped roles (TMEM lanes are rows i, TMEM columns are columns j) and its m / n are swapped.
-struct EpiMode { int vec; int split; int transposed; int mn_n; int mn_m; };   // mn_n / mn_m: the N-side / M-side operand is stored MN-contiguous
+struct EpiMode { int vec; int split; int transposed; int mn_n; int mn_m; int wgroups; };   // mn_n / mn_m: the N-side / M-side operand is stored MN-contiguous
 
 // One thread's 32 accumulators: column j, rows ib .. ib+31.  Fast path when the 32 rows are all
 // inside the matrix and vector access is allowed; otherwise element by element.
@@ -356,10 +362,11 @@ __device__ __forceinline__ float drain32_t(const OutDesc &o, const OutScalars &r
 // (MN = true): raw row r = k-row of 128 codes, eight chunks; chunks 0..3 belong to the first 64-row box of the
 // MN-major BF16 layout, 4..7 to the second.  Either way raw chunk c becomes the BF16 chunks 2c, 2c+1 of a
 // 128-byte row, swizzled with the row index.
-template <int FT, bool MN>
+// NT: number of threads that share the block (ct = 0 .. NT - 1).
+template <int FT, bool MN, int NT = 32 * EPI_WARPS>
 __device__ __forceinline__ void widen_block(const uint8_t *raw, uint8_t *dst, int ct) {
 #pragma unroll
-  for (int idx = ct; idx < 512; idx += 32 * EPI_WARPS) {
+  for (int idx = ct; idx < 512; idx += NT) {
     const uint4 q = *reinterpret_cast<const uint4 *>(raw + idx * 16);
     uint32_t w[8];
     fp8x4_to_bf16x2<FT>(q.x, w[0], w[1]);
@@ -371,6 +378,27 @@ __device__ __forceinline__ void widen_block(const uint8_t *raw, uint8_t *dst, in
     *reinterpret_cast<uint4 *>(row + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     *reinterpret_cast<uint4 *>(row + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
   }
+}
+
+// One 16-byte piece of a K-contiguous FP8 operand (16 codes of row r, chunk c = 0..3 of the 64-code k-block) ->
+// its two BF16 chunks 2c, 2c + 1 of the row's 128 bytes in the 128-byte-swizzled layout (what widen_block does
+// with pieces it reads from shared memory).
+template <int FT>
+__device__ __forceinline__ void widen_piece(const uint4 &q, uint8_t *dst, int r, int c) {
+  uint32_t w[8];
+  fp8x4_to_bf16x2<FT>(q.x, w[0], w[1]);
+  fp8x4_to_bf16x2<FT>(q.y, w[2], w[3]);
+  fp8x4_to_bf16x2<FT>(q.z, w[4], w[5]);
+  fp8x4_to_bf16x2<FT>(q.w, w[6], w[7]);
+  uint8_t *row = dst + r * 128;
+  *reinterpret_cast<uint4 *>(row + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4 *>(row + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+}
+__device__ __forceinline__ uint4 ld_stream16_tc(const void *p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
 }
 
 // ---- host side ---------------------------------------------------------------------------------

@@ -1,7 +1,12 @@
-"""Runs bench.py over every workload and writes a markdown table of the results -- the role
-bench/run_bench.sh + bench/report.py (lines 88-162) play for the reference, without its clock pinning.
+"""Turns bench.py JSON lines into the markdown tables of the documentation -- the role bench/report.py
+(lines 88-162) plays for the reference, without its clock pinning.
 
-    python -m e5m2effma_b200.report [--out report.md] [--steps 20] [--warmup 5]
+    python -m e5m2effma_b200.report FILE [FILE ...]     # files holding one bench.py line each (N = 1, 2, 4, 8 ...)
+    python -m e5m2effma_b200.report --run               # runs `python bench.py` (one GPU) first and reports that
+
+One table per line: for N = 1 every workload of the run (headline first) with time, value, roofline fractions in
+the burst and the sustained regime, clocks and the observed error; for N > 1 the strong-scaling figures of every
+workload (kernel only, with NCCL collectives, with the fused epilogue broadcast).
 """
 import argparse
 import json
@@ -9,34 +14,101 @@ import os
 import subprocess
 import sys
 
-from .workloads import NAMES
-
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def load(path):
+    lines = [l for l in open(path) if l.startswith("{")]
+    if not lines:
+        raise SystemExit(f"{path}: no JSON line")
+    return json.loads(lines[-1])
+
+
+def _pct(x):
+    return "-" if x is None else f"{100 * x:.1f} %"
+
+
+def _err(e):
+    if not e:
+        return "-"
+    parts = []
+    if "accumulation" in e:
+        parts.append(f"{e['accumulation']['max_error_in_units_of_2^-23_sum_abs_products']:.2f} x 2^-23 sum|ab| (FP32 out)")
+    if "output" in e:
+        parts.append(f"{e['output']['max_error_in_output_ulps']:.3f} ulp ({e['output']['output']} out)")
+    return ", ".join(parts) or "-"
+
+
+def single_gpu_table(d):
+    rows = ["| workload | time / step | value | of measured peak | of nominal | sustained: time, of sustained peak, SM MHz | SM MHz (burst), reasons | observed error |",
+            "|---|---|---|---|---|---|---|---|"]
+
+    def row(name, e, err):
+        r = e["roofline"]
+        s = r.get("sustained")
+        sus = "-" if not s else f"{s['ms_per_step'] * 1e3:.1f} us, {_pct(s['frac'])}, {s['clocks'].get('sm_mhz')}"
+        c = e.get("clocks") or {}
+        return (f"| {name} | {e['ms_per_step'] * 1e3:.1f} us | {e['value']:.0f} {e['unit']} | {_pct(r['frac'])} | {_pct(r['frac_of_nominal'])} | {sus} | "
+                f"{c.get('sm_mhz')} {','.join(c.get('reasons', [])) or '-'} | {_err(err)} |")
+
+    rows.append(row(d["config"]["workload"], d, (d.get("cpu_baseline") or {}).get("observed_error")))
+    for name, e in (d.get("workloads") or {}).items():
+        rows.append(f"| {name} | failed: {e['error']} | | | | | | |" if "error" in e else row(e["workload"], e, e.get("observed_error")))
+    out = "\n".join(rows) + "\n"
+    if d.get("e2e"):
+        e = d["e2e"]
+        out += (f"\nEnd to end (host buffers, copies inside the timed region): {e['ms_per_step']:.2f} ms per step = {e['value']:.0f} {e['unit']}; "
+                f"{e['h2d_bytes_per_step'] / 1e6:.1f} MB up, {e['d2h_bytes_per_step'] / 1e6:.1f} MB down per step.\n")
+    if d.get("cpu_baseline"):
+        c = d["cpu_baseline"]
+        out += f"CPU oracle ({c['cores']} threads, {c['kind']}): {c['value']:.3f} {c['unit']} on {c['sample']}.\n"
+    return out
+
+
+def strong_table(d):
+    n = d["n_gpus"]
+    rows = [f"| workload (N = {n}) | T1 (one GPU, full problem) | kernel only: time, T1/(N T) | NCCL collectives: time, T1/(N T) | fused epilogue broadcast: time, T1/(N T) |",
+            "|---|---|---|---|---|"]
+
+    def cell(x):
+        if not x:
+            return "-"
+        if "unavailable" in x:
+            return "unavailable"
+        return f"{x['ms_per_step'] * 1e3:.1f} us, {_pct(x['strong_efficiency'])}"
+
+    def row(name, s):
+        return (f"| {name} | {s['full_problem_one_gpu_ms'] * 1e3:.1f} us | {cell(s.get('kernel_only'))} | {cell(s.get('with_collectives_nccl'))} | "
+                f"{cell(s.get('with_collectives_fused'))} |")
+
+    rows.append(row(d["config"]["workload"], d["strong_scaling"]))
+    for name, e in (d.get("workloads") or {}).items():
+        if "strong_scaling" in e:
+            rows.append(row(e["workload"], e["strong_scaling"]))
+    out = "\n".join(rows) + "\n"
+    if d.get("e2e"):
+        e = d["e2e"]
+        out += (f"\nEnd to end at N = {n}: {e['ms_per_step']:.2f} ms per step = {e['value']:.0f} {e['unit']}; per rank "
+                f"{e.get('h2d_bytes_per_step_per_rank', 0) / 1e6:.1f} MB up, {e.get('d2h_bytes_per_step_per_rank', 0) / 1e6:.1f} MB down.\n")
+    w = d["config"].get("weak")
+    if w:
+        out += f"Weak scaling (every rank the full problem, amax reduced every step): {w['ms_per_step'] * 1e3:.1f} us per step, {w['value']:.0f} {w['unit']}.\n"
+    return out
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="report.md")
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--cpu", action="store_true", help="also time the CPU oracle on every workload (slow)")
+    ap.add_argument("files", nargs="*")
+    ap.add_argument("--run", action="store_true", help="run bench.py on one GPU first and report its line")
     args = ap.parse_args()
-    lines = ["| workload | ms / step | value | of measured peak | of nominal | end to end | clocks (MHz, reasons) |", "|---|---|---|---|---|---|---|"]
-    for name in NAMES:
-        cmd = [sys.executable, os.path.join(ROOT, "bench.py"), "--workload", name, "--steps", str(args.steps), "--warmup", str(args.warmup)]
-        if not args.cpu:
-            cmd.append("--no-cpu")
-        out = subprocess.run(cmd, capture_output=True, text=True)
+    lines = [load(f) for f in args.files]
+    if args.run:
+        out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py")], capture_output=True, text=True)
         if out.returncode != 0:
-            lines.append(f"| {name} | failed: {out.stderr.strip().splitlines()[-1] if out.stderr.strip() else out.returncode} | | | | | |")
-            continue
-        d = json.loads(out.stdout.strip().splitlines()[-1])
-        r, e, c = d["roofline"], d.get("e2e") or {}, d["clocks"]
-        lines.append(f"| {d['config']['workload']} | {d['ms_per_step']:.4f} | {d['value']:.1f} {d['unit']} | {100 * r['frac']:.1f} % | "
-                     f"{100 * r['frac_of_nominal']:.1f} % | {e.get('value', float('nan')):.1f} {d['unit']} | {c['sm_mhz']} {','.join(c['reasons']) or '-'} |")
-        print(lines[-1], flush=True)
-    with open(args.out, "w") as f:
-        f.write("\n".join(lines) + "\n")
+            raise SystemExit(out.stderr[-2000:])
+        lines.append(json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1]))
+    for d in lines:
+        print(single_gpu_table(d) if d["n_gpus"] == 1 else strong_table(d))
 
 
 if __name__ == "__main__":

@@ -129,14 +129,60 @@ def test_rejections():
         f.matmul(rand((16, 24), F8), rand((24, 16), F8))
     with pytest.raises(TypeError):
         f.matmul(a.to(torch.float16), b)
-    with pytest.raises(ValueError, match="shapes do not match"):
+    with pytest.raises(ValueError, match="shapes"):
         f.matmul(a, rand((16, 16), F8))
-    with pytest.raises(ValueError, match="scale_a is only meaningful"):
+    with pytest.raises(ValueError, match="scale_a"):
         f.matmul(a.to(torch.bfloat16), b, scale_a=torch.ones(1, device=DEV))
-    with pytest.raises(ValueError, match="beta != 0"):
+    with pytest.raises(ValueError, match="out must be given"):
         f.matmul(a, b, beta=1.0)
     with pytest.raises(ValueError, match="CUDA tensor"):
         f.cast(torch.zeros(4), F8)
-    with pytest.raises(ValueError, match="step must be >= 1"):
+    with pytest.raises(ValueError, match="step"):
         p = torch.zeros(8, device=DEV)
         f.adam_step(p, p.clone(), p.clone(), p.clone(), lr=1e-3, step=0)
+
+
+def test_rejects_buffers_that_share_memory():
+    """The reference binding refuses an output that overlaps an operand and optimizer arrays that overlap each
+    other (binds/python/csrc/e5m2effma_torch.cpp:90,159-161,247-249)."""
+    f = fx()
+    x = torch.randn(16, 16, device=DEV)
+    with pytest.raises(ValueError, match="share memory"):
+        f.matmul(x, torch.randn(16, 16, device=DEV), out=x)
+    with pytest.raises(ValueError, match="share memory"):
+        f.matmul(torch.randn(16, 16, device=DEV), x.t(), out=x)
+    p, g = torch.zeros(10, device=DEV), torch.zeros(10, device=DEV)
+    m = torch.zeros(10, device=DEV)
+    with pytest.raises(ValueError, match="share memory"):
+        f.adam_step(p, g, m, m, lr=1e-3, step=1)
+    with pytest.raises(ValueError, match="share memory"):
+        f.adam_step(p, p, m, torch.zeros(10, device=DEV), lr=1e-3, step=1)
+    with pytest.raises(ValueError, match="betas"):
+        f.adam_step(p, g, m, torch.zeros(10, device=DEV), lr=1e-3, betas=(0.9, 1.0), step=1)
+    with pytest.raises(ValueError):
+        f.AdamW([torch.nn.Parameter(p)], lr=-1.0)
+
+
+def test_optimizer_skips_empty_parameters():
+    f = fx()
+    w = torch.nn.Parameter(torch.randn(33, device=DEV))
+    e = torch.nn.Parameter(torch.zeros(0, device=DEV))
+    opt = f.AdamW([w, e], lr=1e-2)
+    w.grad, e.grad = torch.randn(33, device=DEV), torch.zeros(0, device=DEV)
+    before = w.detach().clone()
+    opt.step()
+    assert not torch.equal(before, w.detach())
+
+
+def test_rejects_mixed_devices_and_runs_on_the_second_gpu():
+    """binds/python/tests/test_e5m2effma.py:306-318."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    f = fx()
+    a, b = rand((8, 16), F8), rand((16, 8), F8)
+    with pytest.raises(ValueError, match="cuda:1"):
+        f.matmul(a, b.to("cuda:1"))
+    a1, b1 = a.to("cuda:1"), b.to("cuda:1")
+    y = f.matmul(a1, b1)
+    assert y.device == a1.device
+    assert torch.equal(y.cpu(), f.matmul(a, b).cpu())
