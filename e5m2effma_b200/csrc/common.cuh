@@ -234,7 +234,7 @@ enum Opt {
   OPT_GEMV_MT,        // E5MA_GEMV_MT       2: 32 rows per block in the register-load kernel
   OPT_MIXED_PAIR,     // E5MA_MIXED_PAIR    0: FP8 x BF16 problems never take the CTA-pair kernel
   OPT_GEMV_KMAP,      // E5MA_GEMV_KMAP     1: each warp of the cp.async GEMV walks a contiguous eighth of K
-  OPT_WIDEN_GROUPS,   // E5MA_WIDEN_GROUPS  1, 2, 4: groups of warps that widen alternate k-blocks of a mixed FP8 x BF16 GEMM
+  OPT_WIDEN_GROUPS,   // E5MA_WIDEN_GROUPS  1, 2: groups of warps that widen alternate k-blocks of a mixed FP8 x BF16 GEMM
   OPT_COUNT
 };
 int opt(Opt which);

@@ -232,8 +232,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
           const uint8_t *raw = stage + C::J_BYTES + C::I_BYTES;
           uint8_t *dst = stage + (CONV == 1 ? C::J_BYTES : 0);
           const bool mn = CONV == 2 && md.mn_m;
-          if (WG == 4) { if (mn) widen_block<FT, true, 64>(raw, dst, cg); else widen_block<FT, false, 64>(raw, dst, cg); }
-          else if (WG == 2) { if (mn) widen_block<FT, true, 128>(raw, dst, cg); else widen_block<FT, false, 128>(raw, dst, cg); }
+          if (WG == 2) { if (mn) widen_block<FT, true, 128>(raw, dst, cg); else widen_block<FT, false, 128>(raw, dst, cg); }
           else { if (mn) widen_block<FT, true, 256>(raw, dst, cg); else widen_block<FT, false, 256>(raw, dst, cg); }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
           __syncwarp();
@@ -389,11 +388,10 @@ static PairPlan pair_plan(int m, int n, int k, int elem_bytes, int kblocks, int 
     return PairPlan{W, pair_clocks(m, n, kblocks, W, true, sms), true};
   }
   best = PairPlan{256, pair_clocks(m, n, kblocks, 256, false, sms), false};
-  if (forced != 0)
-    for (int W = tc::W_MAX; W >= 320; W -= 64) {
-      const double c = pair_clocks(m, n, kblocks, W, true, sms);
-      if (c < best.clocks) best = PairPlan{W, c, true};
-    }
+  if (forced != 0) {   // full-width tiles only: no narrower width has won a measurement (the tuned table can still name one)
+    const double c = pair_clocks(m, n, kblocks, tc::W_MAX, true, sms);
+    if (c < best.clocks) best = PairPlan{tc::W_MAX, c, true};
+  }
   if (single_clocks(m, n, kblocks, sms) < best.clocks) return PairPlan{0, 0.0, false};
   return best;
 }
@@ -470,8 +468,8 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
     const int ef = trp ? m : n, eb = trp ? n : m;                // extents along the M side (FP8) / N side (BF16)
     const int tiles = ((ef + P_TILE - 1) / P_TILE) * ((eb + P_TILE - 1) / P_TILE);
     if (ef >= 256 && eb >= 256 && (tiles >= sms / 4 || opt(OPT_MIXED_PAIR) == 2)) {
-      CUtensorMap mb[3];
-      if (!make_map(&mb[0], pb, 2, k, eb, ldbf, 128, false) ||
+      CUtensorMap mf, mb[3];
+      if (!make_map(&mf, pf, 1, k, ef, ldf, 128, true) || !make_map(&mb[0], pb, 2, k, eb, ldbf, 128, false) ||
           !make_map(&mb[1], pb, 2, k, eb, ldbf, 64, false) || !make_map(&mb[2], pb, 2, k, eb, ldbf, 32, false))
         return cudaErrorNotSupported;
       const auto vec_okx = [](const void *p, int ld, int dtype) {
@@ -487,10 +485,10 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
       const uint32_t xdesc = instr_desc(1, 1, 256, 256);
       const PairSplit xs = {instr_desc(1, 1, 256, 128), instr_desc(1, 1, 256, 64)};
       const int fdt = trp ? a_dtype : b_dtype;
-      if (trp) return fdt == E5MA_E5M2 ? launch_mixpair_dt<E5MA_E5M2, true>(pf, ldf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s)
-                                       : launch_mixpair_dt<E5MA_E4M3, true>(pf, ldf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s);
-      return fdt == E5MA_E5M2 ? launch_mixpair_dt<E5MA_E5M2, false>(pf, ldf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s)
-                              : launch_mixpair_dt<E5MA_E4M3, false>(pf, ldf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s);
+      if (trp) return fdt == E5MA_E5M2 ? launch_mixpair_dt<E5MA_E5M2, true>(mf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s)
+                                       : launch_mixpair_dt<E5MA_E4M3, true>(mf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s);
+      return fdt == E5MA_E5M2 ? launch_mixpair_dt<E5MA_E5M2, false>(mf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s)
+                              : launch_mixpair_dt<E5MA_E4M3, false>(mf, mb, eb, ef, k, xdesc, xs, o, xm, sms, s);
     }
   }
   // Mixed pairs widen their FP8 operand in shared memory; that costs least when the FP8 operand sits on the
@@ -526,7 +524,7 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   md.mn_n = n_kc ? 0 : 1;
   md.mn_m = m_kc ? 0 : 1;
   md.split = wide && opt(OPT_TC_SPLIT) != 0;
-  md.wgroups = opt(OPT_WIDEN_GROUPS) == 1 || opt(OPT_WIDEN_GROUPS) == 2 || opt(OPT_WIDEN_GROUPS) == 4 ? opt(OPT_WIDEN_GROUPS) : 2;   // measured on B200: 2 groups
+  md.wgroups = opt(OPT_WIDEN_GROUPS) == 1 ? 1 : 2;   // measured on B200: 2 groups (four measured slower)
   md.vec = vec_ok(o.d, o.ldd, o.d_dtype);
   if (o.c && !((o.c_dtype == E5MA_FP32 || o.c_dtype == E5MA_BF16) && vec_ok(o.c, o.ldc, o.c_dtype))) md.vec = 0;
   if (o.bias && !((o.bias_dtype == E5MA_FP32 || o.bias_dtype == E5MA_BF16) && ((uintptr_t)o.bias & 15u) == 0)) md.vec = 0;

@@ -217,10 +217,9 @@ inline WidePlan wide_plan(int W, int tiles, int pairs) {
   p.smem = p.stages * stage_bytes + 1024 + 256;
   const int rest = tiles % pairs;
   p.slices = 1;
-  if (rest > 0 && opt(OPT_TC_SPLIT) != 0) {
-    if (W % 128 == 0 && 4 * rest <= pairs) p.slices = 4;
-    else if (W % 64 == 0 && 2 * rest <= pairs) p.slices = 2;
-  }
+  // Halves only: a quarter slice would run two MMAs of N = W / 8 per 32 bytes of K, and MMAs that narrow cost about
+  // as much as N = 128 ones (measured: 96-wide slices of W = 384 took 1170 clocks per k-block instead of 270).
+  if (rest > 0 && opt(OPT_TC_SPLIT) != 0 && W % 64 == 0 && 2 * rest <= pairs) p.slices = 2;
   return p;
 }
 

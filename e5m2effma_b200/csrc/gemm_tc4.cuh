@@ -1,39 +1,36 @@
 // Tensor-core GEMM on CTA pairs for mixed FP8 x BF16 operand pairs (both K-contiguous): kind::f16 MMAs with
 // M = 256 (the FP8 operand, widened to BF16 in shared memory) x N = 256 (the BF16 operand) per pair.
 //
-// STATUS: correct (its own parity matrix passes) but NOT selected by default -- on B200 it measures 2 to 3 times
-// slower than the one-CTA mixed kernel (4096 x 4096 x 16384: 1518 us against 505 us; a BF16 x BF16 problem of that
-// shape takes 405 us on the FP8 / BF16 pair kernel).  Switching parts of the widening pass off located the cost:
-// with no stores, no proxy fence, a relaxed arrival and no loads the barrier protocol alone runs at 475 us; the
-// release-ordered arrival on the leader's barrier, which must wait for the warp's outstanding global loads of
-// later k-blocks, and those loads themselves account for the rest.  All eight warps of a CTA work on the same
-// k-block, so one such pass per k-block is the pace of the mainloop.  What would fix it -- asynchronous copies
-// (not ordered by the release) into a raw ring, and groups of warps that take k-blocks in turn, as the one-CTA
-// kernel now does -- needs more shared memory than is left beside six 32 KiB stages.  Kept selectable through the
-// MIXED_PAIR switch for further work.
+// STATUS: correct (its own parity matrix passes) but NOT selected by default -- on B200 it measures 1.6 times
+// slower than the one-CTA mixed kernel (4096 x 4096 x 16384: 849 us against 522 us; a BF16 x BF16 problem of that
+// shape takes 405 us on the FP8 / BF16 pair kernel).  Kept selectable through the MIXED_PAIR switch.
 //
-// Why a pair, and why the raw bytes never touch shared memory.  The one-CTA mixed kernel (gemm_tc.cu) keeps a
-// stage -- raw FP8 box, its widened copy and the BF16 box, 56 KiB -- occupied from the moment its TMA loads are
-// issued until its MMAs have retired: about 3000 clocks (load latency, mostly DRAM on a 0.8 GB problem, then
-// widening, then 512 clocks of MMA), and only four such stages fit, i.e. 2048 clocks of MMA work in flight: the
-// tensor pipe idles a third of the time.  Here
-//   * each CTA of the pair holds half of both operands: 128 rows of the FP8 operand (its own 128 TMEM lanes) and
-//     128 of the pair tile's 256 BF16 rows -- 16 KiB widened + 16 KiB BF16 per k-block of 64 instead of 48 KiB,
-//     so six stages fit, and half as many bytes come from L2 and DRAM per FLOP;
-//   * the raw FP8 bytes (8 KiB per k-block and CTA) are fetched by the widening warps themselves with 16-byte
-//     global loads, X_AHEAD k-blocks ahead, into registers: they are in flight without occupying a stage, so an
-//     MMA stage's cycle shrinks to "BF16 load, MMA".  (A raw ring in shared memory fed by TMA was measured first:
-//     three 8 KiB slots were all that fitted beside six stages, far too few to cover the load latency -- 479
-//     TFLOP/s on the 4096 x 4096 x 65536 wgrad problem against 1141 for the one-CTA kernel.)
+// Why a pair: the one-CTA mixed kernel (gemm_tc.cu) keeps a 56 KiB stage -- raw FP8 box, its widened copy and the
+// BF16 box -- occupied from the moment its TMA loads are issued until its MMAs have retired, and only four such
+// stages fit.  In a pair each CTA holds half of both operands: 128 rows of the FP8 operand (its own 128 TMEM lanes)
+// and 128 of the pair tile's 256 BF16 rows -- 16 KiB widened + 16 KiB BF16 per k-block of 64 -- so five stages fit
+// beside a ring of five 8 KiB slots for the raw FP8 boxes (freed as soon as they have been widened), and half as
+// many bytes come from L2 and DRAM per FLOP.
 //
-// Roles per CTA (10 warps): warp 0 loads the BF16 halves by TMA (both CTAs' bytes are counted on the leader's
-// "full" barrier), warps 2..9 widen k-block by k-block from their registers into the MMA stage (fence towards the
-// async proxy, then one arrival per warp on the LEADER's "ready" barrier, remotely from the peer) and drain the
-// accumulator after the tile's last k-block -- the loads of the next tile's first k-blocks are issued before the
-// drain --, warp 1 of the leader issues the MMAs once a stage is both full and ready and commits to both CTAs'
-// "empty" barriers.  Two 256-column accumulators alternate.  Every wait is bounded; a wait that runs out raises the
-// abort flag of both CTAs; the pair meets at a cluster barrier before tensor memory is released.  No load is
-// multicast.
+// What was measured on the way (4096 x 4096 x 16384, E5M2 x BF16 -> FP32):
+//   * raw ring of three slots, all eight warps widening every k-block together: 1280 us.  Too few raw loads in flight.
+//   * no raw ring: the widening warps fetch their 16-byte pieces themselves, six k-blocks ahead, into registers:
+//     1518 us.  Switching parts of the pass off located the cost: the release-ordered arrival on the leader's
+//     barrier must wait for the thread's outstanding global loads of later k-blocks (a relaxed arrival: 1204 us;
+//     no prefetch loads: 1148 us); with no stores, no proxy fence, a relaxed arrival and no loads the barrier
+//     protocol alone still takes 475 us.
+//   * this version -- TMA-fed raw ring of five slots (nothing outstanding in the widening threads), two groups of
+//     four warps taking k-blocks in turn so that two widening passes overlap: 849 us.  What remains is the pass
+//     itself: two barrier waits, shared-memory read, convert, swizzled write, proxy fence and a cluster-scope
+//     release arrival per k-block, in both CTAs, before the leader may issue.
+//
+// Roles per CTA (11 warps): warp 0 loads the BF16 halves (both CTAs' bytes are counted on the leader's "full"
+// barrier), warp 10 loads the raw FP8 boxes (local barrier), warps 2..9 widen into the MMA stage (fence towards the
+// async proxy, then one arrival per warp of the group on the LEADER's "ready" barrier, remotely from the peer) and
+// drain the accumulator after the tile's last k-block, warp 1 of the leader issues the MMAs once a stage is both
+// full and ready and commits to both CTAs' "empty" barriers.  Two 256-column accumulators alternate.  Every wait is
+// bounded; a wait that runs out raises the abort flag of both CTAs; the pair meets at a cluster barrier before
+// tensor memory is released.  No load is multicast.
 //
 // TR = true: the caller swapped the operand roles so that the FP8 operand sits on the M side (an FP8 A): TMEM
 // lanes are rows i of D, TMEM columns are columns j, m / n arrive swapped (as in the one-CTA kernel).
@@ -43,33 +40,39 @@
 namespace e5b {
 namespace tc {
 
-constexpr int X_STAGES = 6;                                   // MMA ring
-constexpr int X_AHEAD = 6;                                    // k-blocks of raw FP8 bytes in flight in registers
+constexpr int X_STAGES = 5;                                   // MMA ring
+constexpr int X_RAW = 5;                                      // raw FP8 ring
+constexpr int X_GROUPS = 2;                                   // groups of widening warps that take k-blocks in turn
 constexpr int X_WIDE_BYTES = 128 * STAGE_K_BYTES;             // widened FP8 half: 128 rows x 64 BF16
 constexpr int X_STAGE_BYTES = X_WIDE_BYTES + P_HALF_BYTES;    // + this CTA's 128 BF16 rows
-constexpr int X_SMEM_BYTES = X_STAGES * X_STAGE_BYTES + 1024 + 512;
-constexpr int X_THREADS = THREADS;
+constexpr int X_RAW_BYTES = 128 * (STAGE_K_BYTES / 2);        // 128 rows x 64 codes
+constexpr int X_SMEM_BYTES = X_STAGES * X_STAGE_BYTES + X_RAW * X_RAW_BYTES + 1024 + 512;
+constexpr int X_THREADS = THREADS + 32;
 
-// F / ldf: the FP8 operand (M side), rows of k codes, pitch ldf bytes.  map_b / map_b2 / map_b4: the BF16
+// map_f: the FP8 operand (M side), boxes of 128 rows x 64 bytes, not swizzled.  map_b / map_b2 / map_b4: the BF16
 // operand (N side), boxes of 128 / 64 / 32 rows x 128 bytes, 128-byte swizzle (whole tiles, slices of the last round).
 template <int DT, int FT, bool TR>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(X_THREADS, 1)
-gemm_tc_mixpair_kernel(const uint8_t *__restrict__ F, int ldf, const __grid_constant__ CUtensorMap map_b,
+gemm_tc_mixpair_kernel(const __grid_constant__ CUtensorMap map_f, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_b4, int m, int n,
                        int k, uint32_t idesc, PairSplit ps, OutDesc o, EpiMode md) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *ring_p = smem_raw + (ring - smem_u32(smem_raw));
-  uint64_t *bars = reinterpret_cast<uint64_t *>(ring_p + X_STAGES * X_STAGE_BYTES);
-  // full[S], empty[S], ready[S], acc_full[2], acc_empty[2]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * X_STAGES + 4);
+  const uint32_t rawring = ring + X_STAGES * X_STAGE_BYTES;
+  uint8_t *rawring_p = ring_p + X_STAGES * X_STAGE_BYTES;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(rawring_p + X_RAW * X_RAW_BYTES);
+  // full[S], empty[S], ready[S], raw_full[R], raw_empty[R], acc_full[2], acc_empty[2]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * X_STAGES + 2 * X_RAW + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   const auto full_bar = [&](int s) { return bar0 + 8u * s; };
   const auto empty_bar = [&](int s) { return bar0 + 8u * (X_STAGES + s); };
   const auto ready_bar = [&](int s) { return bar0 + 8u * (2 * X_STAGES + s); };
-  const auto acc_full = [&](int b) { return bar0 + 8u * (3 * X_STAGES + b); };
-  const auto acc_empty = [&](int b) { return bar0 + 8u * (3 * X_STAGES + 2 + b); };
+  const auto raw_full = [&](int r) { return bar0 + 8u * (3 * X_STAGES + r); };
+  const auto raw_empty = [&](int r) { return bar0 + 8u * (3 * X_STAGES + X_RAW + r); };
+  const auto acc_full = [&](int b) { return bar0 + 8u * (3 * X_STAGES + 2 * X_RAW + b); };
+  const auto acc_empty = [&](int b) { return bar0 + 8u * (3 * X_STAGES + 2 * X_RAW + 2 + b); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
@@ -91,9 +94,10 @@ gemm_tc_mixpair_kernel(const uint8_t *__restrict__ F, int ldf, const __grid_cons
     j0 = tj * P_TILE;
   };
 
-  if (threadIdx.x == 32) { prefetch_map(&map_b); prefetch_map(&map_b2); prefetch_map(&map_b4); }
+  if (threadIdx.x == 32) { prefetch_map(&map_f); prefetch_map(&map_b); prefetch_map(&map_b2); prefetch_map(&map_b4); }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < X_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); mbar_init(ready_bar(s), 2 * EPI_WARPS); }
+    for (int s = 0; s < X_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); mbar_init(ready_bar(s), 2 * EPI_WARPS / X_GROUPS); }
+    for (int r = 0; r < X_RAW; ++r) { mbar_init(raw_full(r), 1); mbar_init(raw_empty(r), EPI_WARPS / X_GROUPS); }
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 2 * EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -129,6 +133,26 @@ gemm_tc_mixpair_kernel(const uint8_t *__restrict__ F, int ldf, const __grid_cons
           if (rank == 0) mbar_expect_tx(full_bar(s), pair_bytes);
           tma_load_2d_pair(ring + s * X_STAGE_BYTES + X_WIDE_BYTES, mb, kb * 64, ir, map_to_rank(full_bar(s), 0));
           if (++s == X_STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == EPI_WARPS + 2) {
+    // ---------------- raw FP8 producer (both CTAs, local ring) ----------------
+    if (lane == 0) {
+      int r = 0;
+      uint32_t rph = 0;
+      bool ok = true;
+      for (int t = pair; t < items && ok; t += pairs) {
+        int i0, j0, cols;
+        item_at(t, i0, j0, cols);
+        const int jr = j0 + (int)rank * 128;
+        const bool backwards = ((t / pairs) & 1) != 0;
+        for (int kq = 0; kq < kblocks; ++kq) {
+          const int kb = backwards ? kblocks - 1 - kq : kq;
+          if (!mbar_wait(raw_empty(r), rph ^ 1u, abort_flag, (6u << 24) | (uint32_t)kb, peer_abort)) { ok = false; break; }
+          mbar_expect_tx(raw_full(r), X_RAW_BYTES);
+          tma_load_2d(rawring + r * X_RAW_BYTES, &map_f, kb * 64, jr, raw_full(r));
+          if (++r == X_RAW) { r = 0; rph ^= 1u; }
         }
       }
     }
@@ -172,55 +196,32 @@ gemm_tc_mixpair_kernel(const uint8_t *__restrict__ F, int ldf, const __grid_cons
     const float as_const = __fmul_rn(o.alpha, o.sa_vec ? 1.f : ld_or_one(o.sa));
     const float sb_const = o.sb_vec ? 1.f : ld_or_one(o.sb);
     float mx = 0.f;
-    int s = 0;
-    uint32_t ph = 0, lt = 0;
+    uint32_t it = 0, lt = 0;     // it: k-blocks since the kernel started (ring positions); lt: tiles of this pair
     bool ok = true;
-    // This thread's two 16-byte pieces of a k-block's raw box: pieces ct and ct + 256 of 512; piece idx is chunk
-    // idx & 3 (16 codes) of row idx >> 2.  Rows beyond the operand and codes beyond k read as zero, like a TMA box.
-    const int r0 = ct >> 2, r1 = (ct + 256) >> 2, cch = (ct & 3) * 16;
-    const auto fetch = [&](int item, int kq, uint4 (&dst)[2]) {
-      int i0, j0, cols;
-      item_at(item, i0, j0, cols);
-      const bool backwards = ((item / pairs) & 1) != 0;
-      const int kc = (backwards ? kblocks - 1 - kq : kq) * 64 + cch;
-      const int ja = j0 + (int)rank * 128 + r0, jb = j0 + (int)rank * 128 + r1;
-      dst[0] = (ja < n && kc < k) ? ld_stream16_tc(F + (size_t)ja * ldf + kc) : make_uint4(0, 0, 0, 0);
-      dst[1] = (jb < n && kc < k) ? ld_stream16_tc(F + (size_t)jb * ldf + kc) : make_uint4(0, 0, 0, 0);
-    };
-    uint4 pre[X_AHEAD][2];
-#pragma unroll
-    for (int u = 0; u < X_AHEAD; ++u)
-      if (pair < items && u < kblocks) fetch(pair, u, pre[u]);
+    // The eight warps form X_GROUPS groups that take k-blocks in turn: one pass over a k-block (two waits, read,
+    // convert, write, proxy fence, remote arrival) is a chain of dependent latencies, and groups overlap such chains.
+    constexpr int GT = 32 * EPI_WARPS / X_GROUPS;
+    const int grp = ct / GT, cg = ct - grp * GT;
     for (int t = pair; t < items && ok; t += pairs, ++lt) {
       int i0, j0, cols;
       item_at(t, i0, j0, cols);
-      for (int kq0 = 0; kq0 < kblocks && ok; kq0 += X_AHEAD) {
-#pragma unroll
-        for (int u = 0; u < X_AHEAD; ++u) {
-          const int kq = kq0 + u;
-          if (kq < kblocks && ok) {      // warp-uniform
-            ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (7u << 24) | (uint32_t)kq, peer_abort);
-            ok = __all_sync(0xFFFFFFFFu, ok);
-            if (ok) {
-              uint8_t *dst = ring_p + s * X_STAGE_BYTES;
-              widen_piece<FT>(pre[u][0], dst, r0, ct & 3);
-              widen_piece<FT>(pre[u][1], dst, r1, ct & 3);
-              if (kq + X_AHEAD < kblocks) fetch(t, kq + X_AHEAD, pre[u]);
-              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
-              __syncwarp();
-              if (lane == 0) mbar_arrive_cluster(map_to_rank(ready_bar(s), 0));
-              if (++s == X_STAGES) { s = 0; ph ^= 1u; }
-            }
-          }
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        if ((int)(it % X_GROUPS) != grp) continue;      // warp-uniform
+        const int s = it % X_STAGES, r = it % X_RAW;
+        const uint32_t ph = (it / X_STAGES) & 1u, rph = (it / X_RAW) & 1u;
+        ok = mbar_wait(raw_full(r), rph, abort_flag, (5u << 24) | (uint32_t)kb, peer_abort) &&
+             mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (7u << 24) | (uint32_t)kb, peer_abort);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        widen_block<FT, false, GT>(rawring_p + r * X_RAW_BYTES, ring_p + s * X_STAGE_BYTES, cg);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(raw_empty(r));
+          mbar_arrive_cluster(map_to_rank(ready_bar(s), 0));
         }
       }
       if (!ok) break;
-      // the next tile's first k-blocks are requested before this tile's accumulator is drained
-      if (t + pairs < items) {
-#pragma unroll
-        for (int u = 0; u < X_AHEAD; ++u)
-          if (u < kblocks) fetch(t + pairs, u, pre[u]);
-      }
       const uint32_t buf = lt & 1u, use = lt >> 1;
       ok = mbar_wait(acc_full(buf), use & 1u, abort_flag, (3u << 24) | (uint32_t)warp, peer_abort);
       ok = __all_sync(0xFFFFFFFFu, ok);
@@ -275,7 +276,7 @@ gemm_tc_mixpair_kernel(const uint8_t *__restrict__ F, int ldf, const __grid_cons
 }
 
 template <int DT, int FT, bool TR>
-static cudaError_t launch_mixpair_cfg(const uint8_t *F, int ldf, const CUtensorMap *mb, int m, int n, int k, uint32_t idesc,
+static cudaError_t launch_mixpair_cfg(const CUtensorMap &mf, const CUtensorMap *mb, int m, int n, int k, uint32_t idesc,
                                       const PairSplit &ps, const OutDesc &o, const EpiMode &md, int sms, cudaStream_t s) {
   static SmemOptIn optin;
   if (const cudaError_t e = optin.ensure(gemm_tc_mixpair_kernel<DT, FT, TR>, X_SMEM_BYTES)) return e;
@@ -283,19 +284,19 @@ static cudaError_t launch_mixpair_cfg(const uint8_t *F, int ldf, const CUtensorM
   int pairs = sms / 2;
   if (tiles < pairs) pairs = tiles;
   note_route(ROUTE_TC_MIXED_PAIR);
-  gemm_tc_mixpair_kernel<DT, FT, TR><<<2 * pairs, X_THREADS, X_SMEM_BYTES, s>>>(F, ldf, mb[0], mb[1], mb[2], m, n, k, idesc, ps, o, md);
+  gemm_tc_mixpair_kernel<DT, FT, TR><<<2 * pairs, X_THREADS, X_SMEM_BYTES, s>>>(mf, mb[0], mb[1], mb[2], m, n, k, idesc, ps, o, md);
   return cudaGetLastError();
 }
 
 template <int FT, bool TR>
-static cudaError_t launch_mixpair_dt(const uint8_t *F, int ldf, const CUtensorMap *mb, int m, int n, int k, uint32_t idesc,
+static cudaError_t launch_mixpair_dt(const CUtensorMap &mf, const CUtensorMap *mb, int m, int n, int k, uint32_t idesc,
                                      const PairSplit &ps, const OutDesc &o, const EpiMode &md, int sms, cudaStream_t s) {
   switch (o.d_dtype) {
-    case E5MA_BF16: return launch_mixpair_cfg<E5MA_BF16, FT, TR>(F, ldf, mb, m, n, k, idesc, ps, o, md, sms, s);
-    case E5MA_FP32: return launch_mixpair_cfg<E5MA_FP32, FT, TR>(F, ldf, mb, m, n, k, idesc, ps, o, md, sms, s);
-    case E5MA_FP16: return launch_mixpair_cfg<E5MA_FP16, FT, TR>(F, ldf, mb, m, n, k, idesc, ps, o, md, sms, s);
-    case E5MA_E5M2: return launch_mixpair_cfg<E5MA_E5M2, FT, TR>(F, ldf, mb, m, n, k, idesc, ps, o, md, sms, s);
-    default: return launch_mixpair_cfg<E5MA_E4M3, FT, TR>(F, ldf, mb, m, n, k, idesc, ps, o, md, sms, s);
+    case E5MA_BF16: return launch_mixpair_cfg<E5MA_BF16, FT, TR>(mf, mb, m, n, k, idesc, ps, o, md, sms, s);
+    case E5MA_FP32: return launch_mixpair_cfg<E5MA_FP32, FT, TR>(mf, mb, m, n, k, idesc, ps, o, md, sms, s);
+    case E5MA_FP16: return launch_mixpair_cfg<E5MA_FP16, FT, TR>(mf, mb, m, n, k, idesc, ps, o, md, sms, s);
+    case E5MA_E5M2: return launch_mixpair_cfg<E5MA_E5M2, FT, TR>(mf, mb, m, n, k, idesc, ps, o, md, sms, s);
+    default: return launch_mixpair_cfg<E5MA_E4M3, FT, TR>(mf, mb, m, n, k, idesc, ps, o, md, sms, s);
   }
 }
 

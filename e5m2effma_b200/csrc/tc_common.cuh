@@ -213,7 +213,7 @@ __device__ __forceinline__ void store32(void *p, const float v[32], float qs) {
 // What the epilogue of one launch needs beyond OutDesc: whether D (and C) admit 16-byte vector
 // access (base and leading dimension multiples of 16 bytes) and whether bias / C have a dtype the
 // vector path reads directly.
-// wgroups: into how many groups the epilogue warps split to widen alternate k-blocks of a mixed problem (1, 2, 4).
+// wgroups: into how many groups the epilogue warps split to widen alternate k-blocks of a mixed problem (1, 2).
 // split: the last partial wave of tiles is cut into half tiles.  transposed: the kernel was given the
 // operands in swapped roles (TMEM lanes are rows i, TMEM columns are columns j) and its m / n are swapped.
 struct EpiMode { int vec; int split; int transposed; int mn_n; int mn_m; int wgroups; };   // mn_n / mn_m: the N-side / M-side operand is stored MN-contiguous

@@ -102,6 +102,7 @@ def allgather_columns(D_full, n, ld_elems, world, align=128, group=None):
         dist.all_gather_into_tensor(D_full[:n], D_full[a:b].clone(), group=group)
     else:
         for r, (a, b) in enumerate(sizes):
-            if b > a:
-                dist.broadcast(D_full[a:b], src=r, group=group)
+            if b > a:       # broadcast takes the GLOBAL rank of the owner, r is its rank within `group`
+                src = r if group is None else dist.get_global_rank(group, r)
+                dist.broadcast(D_full[a:b], src=src, group=group)
     return full

@@ -110,7 +110,7 @@ def test_same_data_without_tail_slices_and_on_single_ctas(case):
 
 
 WIDE_EXTRA = [GemmCase(1, 0, 3584, 3584, 272, E5M2, E4M3, E5M2, -1, BF16, 1.0, 0.0, vec=1, seed=901, tight=True),   # W = 512: 98 tiles, 24 left -> 2 slices
-              GemmCase(1, 0, 4864, 3840, 144, E4M3, E4M3, BF16, -1, -1, 1.25, 1.0, vec=2, seed=902),                  # W = 512: 150 tiles, 2 left -> 4 slices
+              GemmCase(1, 0, 4864, 3840, 144, E4M3, E4M3, BF16, -1, -1, 1.25, 1.0, vec=2, seed=902),                  # W = 512: 150 tiles, 2 left -> 2 slices
               GemmCase(1, 0, 8192, 512, 400, E5M2, E5M2, FP32, BF16, FP32, 1.0, 0.5, vec=3, seed=903, tight=True),    # a column shard: n = 512
               GemmCase(1, 0, 2500, 2100, 528, BF16, BF16, FP16, -1, -1, 1.0, 0.0, seed=904)]
 

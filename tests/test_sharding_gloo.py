@@ -92,3 +92,41 @@ def test_sharded_gemm_matches_unsharded(world, n):
         assert p.exitcode == 0
     res = dict(q.get(timeout=10) for _ in range(world))
     assert all(res.values()), res
+
+
+def _worker_subgroup(rank, world, port, out_q):
+    """Ranks 1 and 2 of a world of 3 form the group that shares a matrix: rank-in-group != global rank, and the
+    uneven column split takes the broadcast path of allgather_columns."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        group = dist.new_group([1, 2])
+        ok = True
+        if rank in (1, 2):
+            gr = dist.get_rank(group)
+            n, m = 72, 8                   # blocks of 16 columns: 48 for group rank 0, 24 for group rank 1
+            full = torch.arange(n * m, dtype=torch.int16).view(n, m)
+            j0, j1 = sharding.split(n, 2, gr, 16)
+            mine = torch.zeros_like(full)
+            mine[j0:j1] = full[j0:j1]
+            sharding.allgather_columns(mine, n, m, 2, align=16, group=group)
+            am = sharding.amax_allreduce(torch.tensor([float(gr + 1)]), group=group)
+            ok = torch.equal(mine, full) and float(am) == 2.0
+        out_q.put((rank, bool(ok)))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gather_inside_a_subgroup():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_subgroup, args=(r, 3, port, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    res = dict(q.get(timeout=10) for _ in range(3))
+    assert all(res.values()), res
