@@ -47,6 +47,18 @@ __device__ __forceinline__ void load8(const void *base, size_t i, float x[8]) {
     }
   }
 }
+// NaN-free groups (the caller has checked): the converter alone is the documented rounding, no patching needed.
+template <int T>
+__device__ __forceinline__ void store8_nonan(void *base, size_t i, const float x[8]) {
+  if (T == E5MA_FP32) {
+    float4 *p = reinterpret_cast<float4 *>(base) + i / 4;
+    __stcs(p, make_float4(x[0], x[1], x[2], x[3]));
+    __stcs(p + 1, make_float4(x[4], x[5], x[6], x[7]));
+  } else {
+    __stcs(reinterpret_cast<uint4 *>(base) + i / 8,
+           make_uint4(cvt_bf16x2_raw(x[0], x[1]), cvt_bf16x2_raw(x[2], x[3]), cvt_bf16x2_raw(x[4], x[5]), cvt_bf16x2_raw(x[6], x[7])));
+  }
+}
 template <int T>
 __device__ __forceinline__ void store8(void *base, size_t i, const float x[8]) {
   if (T == E5MA_FP32) {
@@ -70,6 +82,7 @@ __device__ __forceinline__ float adam_range(const AdamScalars &a, size_t count, 
                                             const void *__restrict__ g_, void *__restrict__ m_, void *__restrict__ v_,
                                             uint8_t *__restrict__ q_, float qs, size_t tid, size_t nthr) {
   float mx = 0.f;
+  const bool qs_finite = fabsf(qs) <= 3.4028234664e38f;   // an infinite scale turns p = 0 into NaN: no shortcut then
   const size_t groups = VEC ? count / 8 : 0;
   for (size_t gi = tid; gi < groups; gi += nthr) {
     const size_t i = gi * 8;
@@ -77,14 +90,29 @@ __device__ __forceinline__ float adam_range(const AdamScalars &a, size_t count, 
     load8<GT>(g_, i, g); load8<PT>(p_, i, p); load8<MT>(m_, i, m); load8<MT>(v_, i, v);
 #pragma unroll
     for (int e = 0; e < 8; ++e) adam_update(a, g[e], p[e], m[e], v[e]);
-    store8<PT>(p_, i, p); store8<MT>(m_, i, m); store8<MT>(v_, i, v);
+    // The hardware converters differ from the documented encoders only for NaN inputs.  One sum over the group's 24
+    // results tells whether any is NaN (a NaN propagates through the adds; Inf - Inf also lands here, harmlessly):
+    // without one -- practically always -- the 24 per-value NaN patches are skipped; the values stored are the same.
+    float chk = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) chk += (p[e] + m[e]) + v[e];
+    const bool clean = qs_finite && !is_nan(chk) && !is_nan(__fmul_rn(chk, qs));   // p = Inf with scale 0 gives NaN too
+    if (clean) { store8_nonan<PT>(p_, i, p); store8_nonan<MT>(m_, i, m); store8_nonan<MT>(v_, i, v); }
+    else { store8<PT>(p_, i, p); store8<MT>(m_, i, m); store8<MT>(v_, i, v); }
     if (QT != -1) {
       constexpr int Q = QT != -1 ? QT : E5MA_E4M3;
       uint32_t w[2];
+      if (clean) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
-        w[h] = enc_fp8x2<Q>(__fmul_rn(p[4 * h], qs), __fmul_rn(p[4 * h + 1], qs)) |
-               (enc_fp8x2<Q>(__fmul_rn(p[4 * h + 2], qs), __fmul_rn(p[4 * h + 3], qs)) << 16);
+        for (int h = 0; h < 2; ++h)
+          w[h] = cvt_fp8x2_raw<Q>(__fmul_rn(p[4 * h], qs), __fmul_rn(p[4 * h + 1], qs)) |
+                 (cvt_fp8x2_raw<Q>(__fmul_rn(p[4 * h + 2], qs), __fmul_rn(p[4 * h + 3], qs)) << 16);
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          w[h] = enc_fp8x2<Q>(__fmul_rn(p[4 * h], qs), __fmul_rn(p[4 * h + 1], qs)) |
+                 (enc_fp8x2<Q>(__fmul_rn(p[4 * h + 2], qs), __fmul_rn(p[4 * h + 3], qs)) << 16);
+      }
       __stcs(reinterpret_cast<uint2 *>(q_ + i), make_uint2(w[0], w[1]));
 #pragma unroll
       for (int e = 0; e < 8; ++e) mx = fmaxf(mx, fabsf(p[e]));

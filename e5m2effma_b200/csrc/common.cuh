@@ -105,6 +105,23 @@ __device__ __forceinline__ uint32_t enc_bf16x2(float lo, float hi) {
   return r;
 }
 __device__ __forceinline__ uint32_t enc_bf16(float v) { return enc_bf16x2(v, 0.f) & 0xFFFFu; }
+// The bare converters, for values the caller knows to be free of NaN (the only inputs the patches above change).
+// The vectorised kernels test a whole group with one sum -- a NaN survives every addition -- and then skip the
+// per-value patches; what is stored is the same.
+__device__ __forceinline__ uint32_t cvt_bf16x2_raw(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+template <int T>
+__device__ __forceinline__ uint32_t cvt_fp8x2_raw(float lo, float hi) {
+  uint32_t r;
+  if (T == E5MA_E4M3)
+    asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f32 t, %1, %2; cvt.u32.u16 %0, t; }" : "=r"(r) : "f"(hi), "f"(lo));
+  else
+    asm("{ .reg .b16 t; cvt.rn.satfinite.e5m2x2.f32 t, %1, %2; cvt.u32.u16 %0, t; }" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
 __device__ __forceinline__ uint32_t enc_f16(float v) { return __half_as_ushort(__float2half_rn(v)); }
 __device__ __forceinline__ uint32_t enc_f16x2(float lo, float hi) { return enc_f16(lo) | (enc_f16(hi) << 16); }
 

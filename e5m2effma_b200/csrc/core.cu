@@ -182,7 +182,8 @@ __device__ __forceinline__ void load16(const void *base, size_t i, float sinv, f
     }
   }
 }
-template <int T, bool WIDE>
+// RAW: the 16 values (and, for an FP8 destination, their products with qs) are known to hold no NaN: bare converters.
+template <int T, bool WIDE, bool RAW = false>
 __device__ __forceinline__ void store16(void *base, size_t i, float qs, const float v[16]) {
   if (WIDE && T == E5MA_FP32) {
     uint8_t *p = reinterpret_cast<uint8_t *>(base) + i * 4;
@@ -196,7 +197,7 @@ __device__ __forceinline__ void store16(void *base, size_t i, float qs, const fl
   } else if (WIDE && (T == E5MA_BF16 || T == E5MA_FP16)) {
     uint32_t w[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) w[e] = T == E5MA_BF16 ? enc_bf16x2(v[2 * e], v[2 * e + 1]) : enc_f16x2(v[2 * e], v[2 * e + 1]);
+    for (int e = 0; e < 8; ++e) w[e] = T == E5MA_BF16 ? (RAW ? cvt_bf16x2_raw(v[2 * e], v[2 * e + 1]) : enc_bf16x2(v[2 * e], v[2 * e + 1])) : enc_f16x2(v[2 * e], v[2 * e + 1]);
     st32B_stream(reinterpret_cast<uint8_t *>(base) + i * 2, w);
   } else if (T == E5MA_FP32) {
     float4 *p = reinterpret_cast<float4 *>(base) + i / 4;
@@ -209,15 +210,17 @@ __device__ __forceinline__ void store16(void *base, size_t i, float qs, const fl
       uint32_t w[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        w[e] = T == E5MA_BF16 ? enc_bf16x2(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]) : enc_f16x2(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
+        w[e] = T == E5MA_BF16 ? (RAW ? cvt_bf16x2_raw(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]) : enc_bf16x2(v[8 * q + 2 * e], v[8 * q + 2 * e + 1])) : enc_f16x2(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
       __stcs(p + q, make_uint4(w[0], w[1], w[2], w[3]));
     }
   } else {
     uint32_t w[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e)
-      w[e] = enc_fp8x2<T>(__fmul_rn(v[4 * e], qs), __fmul_rn(v[4 * e + 1], qs)) |
-             (enc_fp8x2<T>(__fmul_rn(v[4 * e + 2], qs), __fmul_rn(v[4 * e + 3], qs)) << 16);
+      w[e] = RAW ? cvt_fp8x2_raw<T>(__fmul_rn(v[4 * e], qs), __fmul_rn(v[4 * e + 1], qs)) |
+                       (cvt_fp8x2_raw<T>(__fmul_rn(v[4 * e + 2], qs), __fmul_rn(v[4 * e + 3], qs)) << 16)
+                 : enc_fp8x2<T>(__fmul_rn(v[4 * e], qs), __fmul_rn(v[4 * e + 1], qs)) |
+                       (enc_fp8x2<T>(__fmul_rn(v[4 * e + 2], qs), __fmul_rn(v[4 * e + 3], qs)) << 16);
     __stcs(reinterpret_cast<uint4 *>(base) + i / 16, make_uint4(w[0], w[1], w[2], w[3]));
   }
 }
@@ -232,6 +235,8 @@ __global__ void __launch_bounds__(256) cast_kernel(const void *__restrict__ src,
   float mx = 0.f;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthr = (size_t)gridDim.x * blockDim.x;
   constexpr bool VEC = MODE != 0, WIDE = MODE == 2;
+  constexpr bool patched = TD == E5MA_BF16 || is_fp8(TD);     // destinations whose encoders patch NaN
+  const bool qs_finite = fabsf(qs) <= 3.4028234664e38f;
   const size_t groups = VEC ? count / 16 : 0;
   // G groups per step so that every thread keeps 64 bytes of loads in flight whatever the source width
   constexpr int G = 4 / elem_bytes(TS);
@@ -242,9 +247,15 @@ __global__ void __launch_bounds__(256) cast_kernel(const void *__restrict__ src,
     for (int u = 0; u < G; ++u) load16<TS, WIDE>(src, (gidx + u * nthr) * 16, sinv, v[u]);
 #pragma unroll
     for (int u = 0; u < G; ++u) {
+      float chk = 0.f;
 #pragma unroll
-      for (int e = 0; e < 16; ++e) mx = fmaxf(mx, fabsf(v[u][e]));
-      store16<TD, WIDE>(dst, (gidx + u * nthr) * 16, qs, v[u]);
+      for (int e = 0; e < 16; ++e) { mx = fmaxf(mx, fabsf(v[u][e])); chk += v[u][e]; }
+      // one sum tells whether the group holds a NaN (or +Inf and -Inf, or, through an infinite or zero scale, would
+      // produce one): if not, the converters need no NaN patches
+      if (patched && !is_nan(chk) && !(is_fp8(TD) && (!qs_finite || is_nan(__fmul_rn(chk, qs)))))
+        store16<TD, WIDE, true>(dst, (gidx + u * nthr) * 16, qs, v[u]);
+      else
+        store16<TD, WIDE>(dst, (gidx + u * nthr) * 16, qs, v[u]);
     }
   }
   for (; gidx < groups; gidx += nthr) {

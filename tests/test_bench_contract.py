@@ -40,3 +40,27 @@ def test_reference_arm_other_ranks_print_nothing():
                           "--warmup", "0", "--workload", "c3n8"], capture_output=True, text=True, timeout=600, env=e, cwd=ROOT)
     assert out.returncode == 0, out.stderr[-2000:]
     assert not [l for l in out.stdout.splitlines() if l.startswith("{")]
+
+
+def test_roofline_and_sustained_entries_are_self_consistent():
+    """The roofline arithmetic of the benchmark line: achieved = algorithmic units / time, fractions against the
+    measured and the nominal peak, FP8 peak = twice the BF16 figure."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+
+    class W:
+        units = 962.072674304e9
+    pk = {"hbm_gbs": 6500.0, "bf16_tflops": 1600.0, "bf16_tflops_sustained": 1400.0, "source": "measured"}
+    r = bench.roofline("c2", W, 0.35, pk)
+    assert r["bound"] == "tensor" and r["peak"] == 3200.0 and r["nominal_peak"] == 4500.0
+    assert abs(r["achieved"] - 962.072674304 / 0.35) < 1e-6 and abs(r["frac"] - r["achieved"] / 3200.0) < 1e-12
+    assert r["traffic"] == bench.NCU_TRAFFIC_BYTES["c2"] and r["algorithmic_units_per_launch"] == W.units
+    s = bench.sustained_entry("c2", W, 0.4, {"sm_mhz": 1450, "reasons": ["sw_power_cap"]}, 5000, pk)
+    assert s["peak"] == 2800.0 and abs(s["ms_times_mhz"] - 580.0) < 1e-9 and abs(s["frac"] - s["achieved"] / 2800.0) < 1e-12
+    W.units = 67.1e6
+    g = bench.roofline("c3n1", W, 0.016, pk)
+    assert g["bound"] == "hbm" and g["peak"] == 6500.0 and g["nominal_peak"] == 8000.0 and g["unit"] == "GB/s"
+    c4 = bench.roofline("c4", W, 1.0, pk)
+    assert c4["peak"] == 1600.0 and c4["nominal_peak"] == 2250.0

@@ -125,3 +125,45 @@ def test_adam_multi_equals_single_tensor_calls(pt, gt, mt, with_copy):
             assert np.array_equal(from_dev(A[i][slot][0], S[dt], n).view(np.uint8), from_dev(B[i][slot][0], S[dt], n).view(np.uint8)), (i, slot)
         assert np.array_equal(from_dev(A[i][4][0], np.uint8, max(n, 1)), from_dev(B[i][4][0], np.uint8, max(n, 1))), (i, "fp8 copy")
         assert from_dev(A[i][6][0], np.float32, 1)[0] == from_dev(B[i][6][0], np.float32, 1)[0], (i, "amax")
+
+
+@pytest.mark.parametrize("scale", [64.0, 0.0, float("inf")])
+@pytest.mark.parametrize("pt,mt,qt", [(BF16, BF16, E4M3), (FP32, FP32, E5M2), (BF16, FP32, E5M2)])
+def test_adam_special_values_bit_exact(pt, mt, qt, scale):
+    """NaN and Inf in the gradient and the parameter, scales of 0 and Inf for the FP8 copy: the vector path skips the
+    per-value NaN patches of its converters for groups without a NaN, so groups with one -- and the products Inf * 0,
+    0 * Inf that only the scale creates -- must still come out as the oracle's encoders define them."""
+    import torch
+    from e5m2effma_b200 import capi
+    rng = np.random.default_rng(17)
+    n = 8 * 400 + 5
+    cfg = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, step=2, adamw=1, bias_correction=1, grad_scale=1.0)
+    pv = (rng.standard_normal(n) * 0.5).astype(np.float32)
+    gv = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    specials = np.array([np.nan, np.inf, -np.inf, 0.0, -0.0, 3.0e38, -3.0e38, 1e-40], np.float32)
+    pv[rng.integers(0, n, 60)] = specials[rng.integers(0, 8, 60)]
+    gv[rng.integers(0, n, 60)] = specials[rng.integers(0, 8, 60)]
+    p, g = orc.encode(pt, pv), orc.encode(FP32, gv)
+    m = orc.encode(mt, (rng.standard_normal(n) * 0.01).astype(np.float32))
+    v = orc.encode(mt, np.abs(rng.standard_normal(n) * 1e-4).astype(np.float32))
+    bp, pp = to_dev(p); bg, pg = to_dev(g); bm, pm = to_dev(m); bv, pvv = to_dev(v)
+    bq, pq = to_dev(np.zeros(n, np.uint8)); bs, ps = to_dev(np.array([scale], np.float32)); ba, pa = to_dev(np.zeros(1, np.float32))
+    c = capi.AdamConfig(*[cfg[f[0]] for f in capi.AdamConfig._fields_])
+    st = capi.adam(c, n, capi.tensor(pp, pt), capi.tensor(pg, FP32), capi.tensor(pm, mt), capi.tensor(pvv, mt),
+                   capi.tensor(pq, qt, None, ps, pa), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert st == capi.OK, capi.last_error()
+    ep, em, ev, eq = p.copy(), m.copy(), v.copy(), np.zeros(n, np.uint8)
+    eam = orc.adam(cfg, ep, pt, g, FP32, em, ev, mt, eq, qt, scale, 0.0)
+    S = orc.NP_STORAGE
+
+    def same(a, b, t):
+        if t == FP32:      # NaN payloads are not part of the contract
+            return bool(np.all((a.view(np.uint32) == b.view(np.uint32)) | (np.isnan(a) & np.isnan(b))))
+        return np.array_equal(a, b)
+    assert same(from_dev(bp, S[pt], n), ep, pt), "param"
+    assert same(from_dev(bm, S[mt], n), em, mt), "exp_avg"
+    assert same(from_dev(bv, S[mt], n), ev, mt), "exp_avg_sq"
+    assert np.array_equal(from_dev(bq, np.uint8, n), eq), "fp8 copy"
+    am = from_dev(ba, np.float32, 1)[0]
+    assert am == eam or (np.isnan(am) and np.isnan(eam))

@@ -129,3 +129,24 @@ def test_runs_are_deterministic():
     a, am_a = d.run_gpu()
     b, am_b = d.run_gpu()
     assert np.array_equal(a, b) and am_a == am_b
+
+
+@pytest.mark.parametrize("kmap", [0, 1])
+@pytest.mark.parametrize("case", GEMV_CASES[::5] + [GemmCase(1, 0, 2048, 8, 2064, E5M2, BF16, BF16, BF16, -1, 1.0, 0.0, vec=1, seed=33, tight=True),
+                                                    GemmCase(1, 0, 1000, 3, 4112, E4M3, E5M2, FP32, -1, BF16, 1.0, 1.0, vec=3, seed=34)],
+                         ids=lambda c: c.label())
+def test_gemv_k_mappings_within_tolerance(case, kmap):
+    """The cp.async GEMV with interleaved 128-byte k-steps (0) and with each warp on a contiguous eighth of K (1, the
+    tuned default): same results within the bound."""
+    from e5m2effma_b200 import capi
+    if case.bt == FP32:
+        pytest.skip("FP32 x runs the CUDA-core kernel")
+    capi.set_option("GEMV_KMAP", kmap)
+    try:
+        d = GemmData(case)
+        got, amax = d.run_gpu()
+        route = capi.last_route()
+    finally:
+        capi.set_option("GEMV_KMAP", None)
+    check_tolerance(d, got, amax)
+    assert route == capi.ROUTE_GEMV
