@@ -90,7 +90,7 @@ def strong_table(d):
         e = d["e2e"]
         out += (f"\nEnd to end at N = {n}: {e['ms_per_step']:.2f} ms per step = {e['value']:.0f} {e['unit']}; per rank "
                 f"{e.get('h2d_bytes_per_step_per_rank', 0) / 1e6:.1f} MB up, {e.get('d2h_bytes_per_step_per_rank', 0) / 1e6:.1f} MB down.\n")
-    w = d["config"].get("weak")
+    w = d.get("weak_scaling") or (d["config"].get("weak") if isinstance(d["config"].get("weak"), dict) else None)
     if w:
         out += f"Weak scaling (every rank the full problem, amax reduced every step): {w['ms_per_step'] * 1e3:.1f} us per step, {w['value']:.0f} {w['unit']}.\n"
     return out
