@@ -16,6 +16,9 @@ E5M2 row-wise x E4M3 + BF16 bias -> E5M2 + amax) over synthetic, seeded inputs. 
              seconds, until the power-capped clocks have settled, against the sustained peak
   workloads  after the headline, the other configurations of the metric (c1, c3n1, c3n8, c4, c5, one cast) with
              the same protocol: time, value, roofline, clocks
+  gemm_rows  (N = 1) the rows of the reference's own GEMM benchmark at M = N = K = 4096: the four operand layouts
+             TN / NN / NT / TT, the E5M2 x E4M3, E5M2 x BF16 and E5M2 x FP32 pairings and the FP32 accumulate mode,
+             then those of its GEMV benchmark (x in E5M2 / BF16 / FP32, batch 1, 2, 4, 8), each with the kernel that took it
   cpu_baseline  the CPU oracle (a restatement of the reference's host emulation) on a bounded column slab of the
              very operands the GPU just used, all host threads (rank 0, N = 1 only); .observed_error is the
              largest difference between the GPU result and the oracle's double-precision value, in units of
@@ -617,6 +620,73 @@ def measure_sharded(name, w, rot, tm, world, rank, dev, steps, warmup, sampler, 
 
 
 # ---------------------------------------------------------------------------------------------------------------
+ROUTE_NAMES = ["none", "gemv cp.async ring", "gemv bulk-copy ring", "tcgen05 CTA pairs 256x256", "tcgen05 CTA pairs, wide tiles",
+               "tcgen05 one CTA, 256-row tiles", "tcgen05 one CTA, 128-row tiles", "CUDA cores (FP32 FMA chain)", "tcgen05 CTA pairs, mixed", "gemv FP32 activations (FMA pipe)"]
+
+
+def gemm_rows(tm, dev, local, shrink, pk, use_graph):
+    """The rows of the reference's GEMM benchmark (bench/bench_gemm.cu:33-70) at M = N = K = 4096: the four operand
+    layouts of E5M2 x E5M2 -> BF16, then TN with an E4M3, BF16 and FP32 second operand and the FP32 accumulate mode.
+    Each row: event-timed launches over rotating operand sets larger than L2, the kernel that ran, and the fraction
+    of the peak of the unit that kernel runs on."""
+    import torch
+    from e5m2effma_b200 import capi, workloads
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    rows = []
+    torch.cuda.synchronize()
+    time.sleep(1.5)
+    for name in workloads.GEMM_ROWS:
+        w = None
+        try:
+            torch.cuda.empty_cache()
+            w = workloads.make(name, dev, shrink)
+            rot = rotation(w)
+            samp = ClockSampler(local)
+            ms = tm.run(make_step(w, rot), 20, 3, graph=use_graph, sampler=samp)
+            route = capi.last_route()
+            clk = samp.summary()
+            tf = w.units / (ms * 1e-3) / 1e12
+            if route == capi.ROUTE_SIMT:      # the reference's own yardstick: SMs x 128 FMA lanes x the SM clock of this row
+                mhz = clk.get("sm_mhz") or clk.get("sm_max_mhz") or 1965
+                peak, src = sms * 128 * 2 * mhz * 1e6 / 1e12, "FP32 FMA lanes at this row's SM clock"
+            elif w.b_dtype in (capi.E5M2, capi.E4M3):
+                peak, src = 2.0 * pk["bf16_tflops"], f"{pk['source']}: 2 x bf16_tflops burst"
+            else:
+                peak, src = pk["bf16_tflops"], f"{pk['source']}: bf16_tflops burst"
+            rows.append({"row": workloads.GEMM_ROWS[name][0], "ms_per_step": ms, "value": tf, "unit": "TFLOP/s", "kernel": ROUTE_NAMES[route],
+                         "peak": peak, "peak_source": src, "frac": tf / peak, "clocks": clk})
+        except Exception as e:
+            rows.append({"row": workloads.GEMM_ROWS[name][0], "error": f"{type(e).__name__}: {str(e)[:300]}"})
+        finally:
+            del w
+    return rows
+
+
+def gemv_rows(tm, dev, local, shrink, pk, use_graph):
+    """The rows of the reference's GEMV benchmark (bench/bench_gemv.cu:38-47) on C3's weights (8192 x 8192 E5M2,
+    row-wise scales): x in E5M2, BF16 and FP32, batch 1, 2, 4, 8.  GB/s of algorithmic bytes (W once, x, scales, y)."""
+    import torch
+    from e5m2effma_b200 import capi, workloads
+    rows = []
+    torch.cuda.synchronize()
+    time.sleep(1.5)
+    for name in workloads.GEMV_ROWS:
+        w = None
+        try:
+            torch.cuda.empty_cache()
+            w = workloads.make(name, dev, shrink)
+            samp = ClockSampler(local)
+            ms = tm.run(make_step(w, rotation(w)), 20, 3, graph=use_graph, sampler=samp)
+            gbs = w.units / (ms * 1e-3) / 1e9
+            rows.append({"row": workloads.GEMV_ROWS[name][0], "ms_per_step": ms, "value": gbs, "unit": "GB/s", "kernel": ROUTE_NAMES[capi.last_route()],
+                         "peak": pk["hbm_gbs"], "peak_source": f"{pk['source']}: hbm_gbs (copy)", "frac": gbs / pk["hbm_gbs"], "clocks": samp.summary()})
+        except Exception as e:
+            rows.append({"row": workloads.GEMV_ROWS[name][0], "error": f"{type(e).__name__}: {str(e)[:300]}"})
+        finally:
+            del w
+    return rows
+
+
 def run_reference(args, metric, unit, config):
     """The reference's CPU algorithm (oracle port) on the same seeded inputs, all host threads; rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
@@ -938,6 +1008,12 @@ def main():
                 del del_w
         fault = fault or capi.gemm_fault()
 
+    # ---- the layout and pairing rows of the reference's GEMM benchmark (N = 1) ----
+    rows = None
+    if world == 1 and not args.no_extras and name == "c2":
+        rows = gemm_rows(tm, dev, local, args.shrink, pk, use_graph) + gemv_rows(tm, dev, local, args.shrink, pk, use_graph)
+        fault = fault or capi.gemm_fault()
+
     # ---- sustained regime of the headline (N = 1) ----
     if world == 1 and not args.no_extras and args.sustain_s > 0:
         s_ms, s_clk, s_launches = tm.sustained(step_full, t1_ms, ClockSampler(local), args.sustain_s)
@@ -978,6 +1054,8 @@ def main():
     line.update(line_extra)
     if others is not None:
         line["workloads"] = others
+    if rows is not None:
+        line["gemm_rows"] = rows
     print(json.dumps(line), flush=True)
     finish()
 

@@ -264,7 +264,7 @@ int tuned_gemv(int key);
 
 // Which kernel the last e5ma_gemm call of this host thread launched (e5b_last_route()).
 enum Route { ROUTE_NONE = 0, ROUTE_GEMV = 1, ROUTE_GEMV_PERSISTENT = 2, ROUTE_TC_PAIR = 3, ROUTE_TC_PAIR_WIDE = 4,
-             ROUTE_TC_256 = 5, ROUTE_TC_128 = 6, ROUTE_SIMT = 7, ROUTE_TC_MIXED_PAIR = 8 };
+             ROUTE_TC_256 = 5, ROUTE_TC_128 = 6, ROUTE_SIMT = 7, ROUTE_TC_MIXED_PAIR = 8, ROUTE_GEMV_F32X = 9 };
 void note_route(int r);
 // E5MA_OK and the properties of the current device when it is compute capability 10.x
 e5ma_status require_blackwell(const char *who, DeviceProps *out);

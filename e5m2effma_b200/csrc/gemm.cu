@@ -1,5 +1,5 @@
 // e5ma_gemm: argument validation, output description, and the choice between the three kernels:
-//   * the streaming GEMV kernel          (n <= 8, both operands K-contiguous, FP8 A; gemv.cu)
+//   * the streaming GEMV kernels         (n <= 8, both operands K-contiguous, FP8 A, any x dtype; gemv.cu)
 //   * the tcgen05 tensor-core kernel      (FP8 / BF16 operand pairs; gemm_tc.cu)
 //   * the CUDA-core kernel in this file   (FP32 operands and every shape the others decline)
 //
@@ -150,7 +150,7 @@ static e5ma_status gemm_impl(e5ma_op transa, e5ma_op transb, int m, int n, int k
   // switch FORCE_SIMT (experiments and tests): every problem takes the ascending-k CUDA-core kernel
   note_route(ROUTE_NONE);
   if (opt(OPT_FORCE_SIMT) == 1) { /* keep err: falls through to the CUDA-core kernel */ }
-  else if (n <= 8 && a_kc && b_kc && is_fp8(A->dtype) && B->dtype != E5MA_FP32 && k > 0)
+  else if (n <= 8 && a_kc && b_kc && is_fp8(A->dtype) && k > 0)
     err = launch_gemv_mma(A->dtype, B->dtype, a, lda, b, ldb, m, n, k, o, dp.sms, stream);
   else if (A->dtype != E5MA_FP32 && B->dtype != E5MA_FP32 && k > 0)
     err = launch_gemm_tc(A->dtype, B->dtype, a_kc, b_kc, a, lda, b, ldb, m, n, k, o, dp.sms, stream);

@@ -416,7 +416,15 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   // lowest estimated time wins (pair_plan below); the one-CTA kernel stays for everything else.
   const bool use_pair = opt(OPT_TC_PAIR) != 0;   // experiments: 0 keeps every problem on single CTAs
   const int kblocks = (k * (f8 ? 1 : 2) + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
-  const PairPlan plan = use_pair && a_kc && b_kc && conv == 0 ? pair_plan(m, n, k, f8 ? 1 : 2, kblocks, sms) : PairPlan{0, 0.0, false};
+  PairPlan plan = use_pair && a_kc && b_kc && conv == 0 ? pair_plan(m, n, k, f8 ? 1 : 2, kblocks, sms) : PairPlan{0, 0.0, false};
+  // An epilogue that also copies its block to peers hides that copy only behind the mainloop of a later tile.  Wide
+  // tiles that fill a single round leave all of it exposed; 256 x 256 tiles over the same problem run two rounds
+  // in the same mainloop time, and the first round's copies travel during the second.
+  if (o.npeers > 0 && plan.wide && opt(OPT_TC_WIDE) < 0) {
+    const int wide_tiles = ((m + plan.W - 1) / plan.W) * ((n + P_TILE - 1) / P_TILE);
+    const int tiles256 = ((m + P_TILE - 1) / P_TILE) * ((n + P_TILE - 1) / P_TILE);
+    if (wide_tiles <= sms / 2 && tiles256 > sms / 2) plan = PairPlan{P_TILE, pair_clocks(m, n, kblocks, P_TILE, false, sms), false};
+  }
   if (plan.W > 0) {
     const int fi2 = f8 ? (a_dtype == E5MA_E5M2 ? 1 : 0) : 1, fj2 = f8 ? (b_dtype == E5MA_E5M2 ? 1 : 0) : 1;
     const auto vec_ok2 = [](const void *p, int ld, int dtype) {

@@ -269,6 +269,109 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_async_kernel(const uint8_t
   if (o.amax) block_amax(o.amax, mx);
 }
 
+// ---- FP32 activations: the same stream on the FP32 pipe ------------------------------------------
+// An FP32 X does not fit a tensor-core operand without splitting it, and the reference sends this case to its
+// bandwidth kernel like every other skinny problem with FP8 weights (src/gemm_e5m2effma.cu:100-102), where each
+// product is one FP32 FMA (src/gemv_e5m2effma.cuh:27-79).  So does this kernel: a block owns 16 rows; a warp
+// owns R of them over 1 / KS of K and walks it 512 bytes at a time (16 bytes per lane and row, the next step's
+// loads issued before this step's arithmetic); every lane keeps R x NC running sums of its own k positions (one
+// FMA per product, exact decode of W), a butterfly adds the lanes, the KS parts meet in shared memory in a fixed
+// order and 128 threads run the common epilogue.  NC = n rounded up to 1, 2, 4, 8 sizes the register tile.
+template <int AT, int NC, int R>
+__global__ void __launch_bounds__(GV_WARPS * 32) gemv_f32x_kernel(const uint8_t *__restrict__ W, int lda,
+                                                                  const float *__restrict__ X, int ldx, int m, int n, int k,
+                                                                  OutDesc o) {
+  constexpr int GROUPS = 16 / R, KS = GV_WARPS / GROUPS;
+  __shared__ float red[KS][16][9];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int grp = warp % GROUPS, ks = warp / GROUPS;
+  const int row0 = blockIdx.x * 16 + grp * R;
+  const int chunks = (k + 511) / 512, per = (chunks + KS - 1) / KS;
+  const int kbeg = ks * per * 512, kend = (ks + 1) * per * 512 < k ? (ks + 1) * per * 512 : k;
+
+  const uint8_t *wrow[R];
+  bool live[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    live[r] = row0 + r < m;
+    wrow[r] = W + (size_t)(live[r] ? row0 + r : 0) * lda;
+  }
+  float acc[R][NC];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int j = 0; j < NC; ++j) acc[r][j] = 0.f;
+
+  uint4 cur[R], nxt[R];
+  const auto load_w = [&](uint4 (&q)[R], int k0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) q[r] = live[r] && k0 < kend ? ld_stream16(wrow[r] + k0) : make_uint4(0, 0, 0, 0);
+  };
+  load_w(cur, kbeg + lane * 16);
+  for (int kb = kbeg; kb < kend; kb += 512) {
+    const int k0 = kb + lane * 16;
+    load_w(nxt, k0 + 512);
+    const bool in = k0 < kend;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {          // one 32-bit word of every row: four codes against four floats of every column
+      float wf[R][4];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const uint32_t word = q == 0 ? cur[r].x : q == 1 ? cur[r].y : q == 2 ? cur[r].z : cur[r].w;
+        fp8x4_to_f32<AT>(word, wf[r]);
+      }
+#pragma unroll
+      for (int j = 0; j < NC; ++j) {
+        const float4 x = in && j < n ? __ldg(reinterpret_cast<const float4 *>(X + (size_t)j * ldx + k0 + 4 * q)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          acc[r][j] = __fmaf_rn(wf[r][0], x.x, acc[r][j]);
+          acc[r][j] = __fmaf_rn(wf[r][1], x.y, acc[r][j]);
+          acc[r][j] = __fmaf_rn(wf[r][2], x.z, acc[r][j]);
+          acc[r][j] = __fmaf_rn(wf[r][3], x.w, acc[r][j]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) cur[r] = nxt[r];
+  }
+
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      float v = acc[r][j];
+#pragma unroll
+      for (int d = 16; d; d >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
+      if (lane == r * NC + j) red[ks][grp * R + r][j] = v;
+    }
+  __syncthreads();
+  const OutScalars sc = out_begin(o);
+  float mx = 0.f;
+  if (threadIdx.x < 128) {
+    const int il = threadIdx.x & 15, j = threadIdx.x >> 4, i = blockIdx.x * 16 + il;
+    if (i < m && j < n) {
+      float s = red[0][il][j];
+#pragma unroll
+      for (int p = 1; p < KS; ++p) s = __fadd_rn(s, red[p][il][j]);
+      mx = out_store(o, sc, i, j, s);
+    }
+  }
+  if (o.amax) block_amax(o.amax, mx);
+}
+
+template <int AT>
+static cudaError_t gemv_f32x(const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k, const OutDesc &o,
+                             cudaStream_t s) {
+  const unsigned grid = (unsigned)((m + 15) / 16);
+  const float *x = reinterpret_cast<const float *>(X);
+  if (n == 1) gemv_f32x_kernel<AT, 1, 4><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, x, ldx, m, n, k, o);
+  else if (n == 2) gemv_f32x_kernel<AT, 2, 4><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, x, ldx, m, n, k, o);
+  else if (n <= 4) gemv_f32x_kernel<AT, 4, 2><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, x, ldx, m, n, k, o);
+  else gemv_f32x_kernel<AT, 8, 2><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, x, ldx, m, n, k, o);
+  return cudaGetLastError();
+}
+
 // ---- persistent kernel with a bulk-copy weight ring ------------------------------------------------
 // One CTA per SM walks over 16-row tiles of W.  A producer warp streams the tile's rows into a ring of
 // shared-memory stages with bulk asynchronous copies (16 rows x 1 KiB per stage, one copy per row, completion
@@ -607,6 +710,12 @@ cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda,
   // Persistent bulk-copy kernel: only on request (switch GEMV_KERNEL = 2) and when X fits beside a ring of at
   // least three stages.  Measured on B200 (8192 x 8192 weights): 24 us against 15.6 us for the cp.async kernel --
   // bulk copies keep too few bytes in flight per SM, whatever their size.
+  if (x_dtype == E5MA_FP32) {
+    note_route(ROUTE_GEMV_F32X);
+    if (a_dtype == E5MA_E5M2) return gemv_f32x<E5MA_E5M2>(A, lda, X, ldx, m, n, k, o, s);
+    if (a_dtype == E5MA_E4M3) return gemv_f32x<E5MA_E4M3>(A, lda, X, ldx, m, n, k, o, s);
+    return cudaErrorNotSupported;
+  }
   const int which = opt(OPT_GEMV_KERNEL) >= 0 ? opt(OPT_GEMV_KERNEL) : tuned_gemv(0);
   const BulkPlan bp = gemv_bulk_plan(n, k);
   if (bp.stages && which == 2) {

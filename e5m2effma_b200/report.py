@@ -6,7 +6,8 @@
 
 One table per line: for N = 1 every workload of the run (headline first) with time, value, roofline fractions in
 the burst and the sustained regime, clocks and the observed error; for N > 1 the strong-scaling figures of every
-workload (kernel only, with NCCL collectives, with the fused epilogue broadcast).
+workload (kernel only, with NCCL collectives, with the fused epilogue broadcast).  A line that carries `gemm_rows`
+(the layout and pairing rows of the reference's GEMM benchmark) gets a third table.
 """
 import argparse
 import json
@@ -65,6 +66,19 @@ def single_gpu_table(d):
     return out
 
 
+def rows_table(d):
+    """The layout / pairing rows of the reference's GEMM benchmark (bench/bench_gemm.cu:33-70, M = N = K = 4096) and
+    the rows of its GEMV benchmark (bench/bench_gemv.cu:38-47, 8192 x 8192 weights)."""
+    rows = ["| row | time | value | kernel | of that unit's peak | SM MHz |", "|---|---|---|---|---|---|"]
+    for r in d.get("gemm_rows") or []:
+        if "error" in r:
+            rows.append(f"| {r['row']} | failed: {r['error']} | | | | |")
+        else:
+            rows.append(f"| {r['row']} | {r['ms_per_step'] * 1e3:.1f} us | {r['value']:.0f} {r['unit']} | {r['kernel']} | "
+                        f"{_pct(r['frac'])} of {r['peak']:.0f} ({r['peak_source']}) | {(r.get('clocks') or {}).get('sm_mhz')} |")
+    return "\n".join(rows) + "\n"
+
+
 def strong_table(d):
     n = d["n_gpus"]
     rows = [f"| workload (N = {n}) | T1 (one GPU, full problem) | kernel only: time, T1/(N T) | NCCL collectives: time, T1/(N T) | fused epilogue broadcast: time, T1/(N T) |",
@@ -109,6 +123,8 @@ def main():
         lines.append(json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1]))
     for d in lines:
         print(single_gpu_table(d) if d["n_gpus"] == 1 else strong_table(d))
+        if d.get("gemm_rows"):
+            print(rows_table(d))
 
 
 if __name__ == "__main__":

@@ -71,20 +71,27 @@ def randn_chunked(shape, std, seed, dev, out_dtype=torch.float32, chunk_rows=204
 
 
 class GemmWorkload:
-    """e5ma_gemm with both operands K-contiguous (the FP8 layout): A is [m, k] row-major storage
+    """e5ma_gemm, by default with both operands K-contiguous (the FP8 layout): A is [m, k] row-major storage
     (column-major k x m, transa = T), B is [n, k] (transb = N), D is [n, m] storage (column-major
-    m x n, ldd = m)."""
+    m x n, ldd = m).  transa = "N" stores A as [k, m] (lda = m), transb = "T" stores B as [k, n] (ldb = n): the
+    same values, so the four layouts of one problem produce the same D."""
 
     kind = "gemm"
 
     def __init__(self, name, m, n, k, a_dtype, b_dtype, d_dtype, dev, a_std=1.0, b_std=1.0, a_uniform=None,
                  b_uniform=None, a_scaling="fixed", b_scaling="fixed", a_scale_inv=1.0, b_scale_inv=1.0, bias_std=None,
-                 beta=0.0, d0_std=None, d_scale=None, want_amax=False, seed=0):
+                 beta=0.0, d0_std=None, d_scale=None, want_amax=False, seed=0, transa="T", transb="N"):
         self.name, self.m, self.n, self.k = name, m, n, k
+        self.transa, self.transb = transa, transb
+        self.lda, self.ldb = (k if transa == "T" else m), (k if transb == "N" else n)
         self.a_dtype, self.b_dtype, self.d_dtype = a_dtype, b_dtype, d_dtype
         self.beta, self.dev = beta, dev
         self.A, self.sa, self.a_outer = self._operand((m, k), a_dtype, a_std, a_uniform, a_scaling, a_scale_inv, seed + 1)
         self.B, self.sb, self.b_outer = self._operand((n, k), b_dtype, b_std, b_uniform, b_scaling, b_scale_inv, seed + 2)
+        if transa != "T":
+            self.A = self.A.t().contiguous()
+        if transb != "N":
+            self.B = self.B.t().contiguous()
         self.bias = None
         if bias_std is not None:
             self.bias = (torch.randn(m, generator=_gen(seed + 3, dev), device=dev) * bias_std).to(torch.bfloat16)
@@ -101,8 +108,8 @@ class GemmWorkload:
 
     def _operand(self, shape, dtype, std, uniform, scaling, scale_inv, seed):
         dev = self.dev
-        if dtype == capi.BF16:
-            return randn_chunked(shape, std, seed, dev, torch.bfloat16), None, False
+        if dtype in (capi.BF16, capi.FP32):
+            return randn_chunked(shape, std, seed, dev, TORCH_DT[dtype]), None, False
         if uniform is not None:
             x = (torch.rand(shape, generator=_gen(seed, dev), device=dev) * 2 - 1) * uniform
         else:
@@ -134,8 +141,8 @@ class GemmWorkload:
 
     def launch(self, stream, A=None, B=None, D=None):
         tA, tB, tD, tb = self.tensors(A, B, D)
-        _check(capi.gemm(capi.OP_T, capi.OP_N, self.m, self.n, self.k, 1.0, tA, self.k, tB, self.k, self.beta, None, 0,
-                         tD, self.m, tb, stream), "e5ma_gemm")
+        _check(capi.gemm(capi.OP_T if self.transa == "T" else capi.OP_N, capi.OP_N if self.transb == "N" else capi.OP_T,
+                         self.m, self.n, self.k, 1.0, tA, self.lda, tB, self.ldb, self.beta, None, 0, tD, self.m, tb, stream), "e5ma_gemm")
 
     launches_per_pass = 1
 
@@ -249,6 +256,18 @@ def make(name, dev, shrink=1):
     if name == "c4":      # wgrad: E5M2 gradient (scale 1) x BF16 activations, accumulated into FP32 main_grad
         return GemmWorkload("c4", 4096 // s, 4096 // s, 65536 // s, capi.E5M2, capi.BF16, capi.FP32, dev, a_std=1e-3,
                             a_scale_inv=1.0, b_std=1.0, beta=1.0, d0_std=1e-4, seed=4000)
+    if name in GEMM_ROWS:  # the rows of the reference's GEMM benchmark (bench/bench_gemm.cu:33-70): M = N = K = 4096, C1's values
+        ta, tb, bt, dt, beta = GEMM_ROWS[name][1:]
+        return GemmWorkload(name, 4096 // s, 4096 // s, 4096 // s, capi.E5M2, bt, dt, dev, a_std=8.0, a_scale_inv=0.125,
+                            b_std=8.0 if bt in FP8_MAX else 1.0, b_scale_inv=0.125 if bt in FP8_MAX else 1.0, beta=beta,
+                            d0_std=1e-2 if beta else None, seed=7000, transa=ta, transb=tb)
+    if name in GEMV_ROWS:  # the rows of the reference's GEMV benchmark (bench/bench_gemv.cu:38-47): C3's weights, x in three formats
+        xt, nb = GEMV_ROWS[name][1:]
+        w = GemmWorkload(name, 8192 // s, nb, 8192 // s, capi.E5M2, xt, capi.BF16, dev, a_std=0.02, a_scaling="outer",
+                         b_std=1.0, b_scaling="tensor", seed=3000)
+        w.units = float(w.m) * w.k + float(w.B.element_size()) * w.k * nb + 4.0 * w.m + 2.0 * w.m * nb
+        w.unit_name = "B"
+        return w
     if name == "c5":      # AdamW over 2^30 BF16 parameters with an E4M3 copy
         return AdamWorkload("c5", (1 << 30) // s, dev, seed=5000)
     if name == "cast_f32_e5m2":
@@ -266,5 +285,21 @@ def finish_c2(w, prev_amax):
     w.amax.zero_()
     return w
 
+
+# name -> (description, transa, transb, B dtype, D dtype, beta): the rows of the reference's GEMM benchmark
+GEMM_ROWS = {
+    "row_tn": ("e5ma_gemm TN E5M2 x E5M2 -> BF16", "T", "N", capi.E5M2, capi.BF16, 0.0),
+    "row_nn": ("e5ma_gemm NN E5M2 x E5M2 -> BF16", "N", "N", capi.E5M2, capi.BF16, 0.0),
+    "row_nt": ("e5ma_gemm NT E5M2 x E5M2 -> BF16", "N", "T", capi.E5M2, capi.BF16, 0.0),
+    "row_tt": ("e5ma_gemm TT E5M2 x E5M2 -> BF16", "T", "T", capi.E5M2, capi.BF16, 0.0),
+    "row_tn_e4m3": ("e5ma_gemm TN E5M2 x E4M3 -> BF16", "T", "N", capi.E4M3, capi.BF16, 0.0),
+    "row_tn_bf16": ("e5ma_gemm TN E5M2 x BF16 -> BF16", "T", "N", capi.BF16, capi.BF16, 0.0),
+    "row_tn_f32": ("e5ma_gemm TN E5M2 x FP32 -> BF16", "T", "N", capi.FP32, capi.BF16, 0.0),
+    "row_tn_bf16_acc": ("e5ma_gemm TN E5M2 x BF16, FP32 D += (accumulate)", "T", "N", capi.BF16, capi.FP32, 1.0),
+}
+
+# name -> (description, x dtype, batch): the rows of the reference's GEMV benchmark
+GEMV_ROWS = {f"gemv_{xn.lower()}_n{nb}": (f"e5ma gemv n={nb} x={xn} -> BF16", xt, nb)
+             for xn, xt in (("E5M2", capi.E5M2), ("BF16", capi.BF16), ("FP32", capi.FP32)) for nb in (1, 2, 4, 8)}
 
 NAMES = ["c1", "c2", "c3n1", "c3n8", "c4", "c5", "cast_f32_e5m2", "cast_bf16_e4m3", "cast_e4m3_bf16"]

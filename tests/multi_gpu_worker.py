@@ -44,6 +44,7 @@ def main():
             args = (capi.OP_T, capi.OP_N, w.m, sh.n, w.k, 1.0, tA, w.k, sh.B, w.k, 0.0, None, 0, sh.D, w.m, tb)
             off = sh.j0 * w.m * es
         assert capi.gemm(*args, stream) == capi.OK, capi.last_error()
+        plain_route = capi.last_route()
         if w.n <= 8:                                     # row blocks of each column: gather column by column
             for j in range(w.n):
                 col = w.D[j]
@@ -68,8 +69,13 @@ def main():
         dist.barrier()
         fused = pb.local[: w.D.numel() * es].view(w.D.dtype).view(w.D.shape).clone()
 
-        if not torch.equal(nccl.view(torch.uint8), fused.view(torch.uint8)):
-            failures.append(f"{name}: NCCL-gathered and epilogue-broadcast outputs differ")
+        if capi.last_route() == plain_route:
+            if not torch.equal(nccl.view(torch.uint8), fused.view(torch.uint8)):
+                failures.append(f"{name}: NCCL-gathered and epilogue-broadcast outputs differ")
+        else:             # the broadcasting launch may prefer another tile shape (more rounds to hide the copies behind)
+            diff = (nccl.view(torch.int16).int() - fused.view(torch.int16).int()).abs()
+            if int(diff.max()) > 1 or float((diff != 0).float().mean()) > 0.02:
+                failures.append(f"{name}: NCCL-gathered and epilogue-broadcast outputs differ by more than one code")
         if w.n <= 8:      # a row's sum does not depend on how many rows the call has: bit for bit
             if not torch.equal(nccl.view(torch.uint8), full.view(torch.uint8)):
                 failures.append(f"{name}: gathered row shards differ from the unsharded GEMV")

@@ -32,7 +32,7 @@ def _check_columns(w, cols, k_eps=1.0):
     qs = float(w.d_scale.item()) if w.d_scale is not None else 1.0
     amax_seen = 0.0
     for j0, j1 in cols:
-        ref, mag, fix = orc.gemm_wide(1, 0, w.m, w.n, w.k, 1.0, A, w.a_dtype, w.k, B, w.b_dtype, w.k, w.beta, C0, w.d_dtype,
+        ref, mag, fix = orc.gemm_wide(int(w.transa == "T"), int(w.transb == "T"), w.m, w.n, w.k, 1.0, A, w.a_dtype, w.lda, B, w.b_dtype, w.ldb, w.beta, C0, w.d_dtype,
                                       w.m, bias=bias, bias_dtype=orc.BF16, a_sinv=sa, a_outer=w.a_outer, b_sinv=sb,
                                       b_outer=w.b_outer, cols=(j0, j1))
         bound = w.k * 2.0 ** -23 * mag * k_eps + 2.0 ** -21 * (np.abs(ref) + fix + mag)
@@ -78,12 +78,13 @@ def test_c2_hybrid_dgrad_sampled_columns():
     assert float(w.amax.item()) >= seen * (1 - 2.0 ** -7) and abs(float(w.amax.item()) - prev_amax) <= prev_amax * 2.0 ** -6
 
 
-@pytest.mark.parametrize("name", ["c3n1", "c3n8"])
+@pytest.mark.parametrize("name", ["c3n1", "c3n8", "gemv_e5m2_n4", "gemv_fp32_n1", "gemv_fp32_n2", "gemv_fp32_n4", "gemv_fp32_n8"])
 def test_c3_decode_gemv_whole_output(name):
     import torch
-    from e5m2effma_b200 import workloads
+    from e5m2effma_b200 import capi, workloads
     w = workloads.make(name, torch.device("cuda", 0))
     _run(w)
+    assert capi.last_route() == (capi.ROUTE_GEMV_F32X if w.b_dtype == capi.FP32 else capi.ROUTE_GEMV)
     _check_columns(w, [(0, w.n)])
 
 
@@ -93,6 +94,36 @@ def test_c4_wgrad_accumulate_sampled_columns():
     w = workloads.make("c4", torch.device("cuda", 0))
     _run(w)
     _check_columns(w, [(0, 4), (2046, 2050), (4092, 4096)])
+
+
+@pytest.mark.parametrize("name", ["row_tn", "row_nn", "row_nt", "row_tt", "row_tn_e4m3", "row_tn_bf16", "row_tn_f32", "row_tn_bf16_acc"])
+def test_reference_benchmark_rows_sampled_columns(name):
+    """The 4096^3 rows of the reference's GEMM benchmark (four layouts, the pairings, accumulate mode): sampled columns
+    against the oracle, and the kernel each row is expected to take."""
+    import torch
+    from e5m2effma_b200 import capi, workloads
+    w = workloads.make(name, torch.device("cuda", 0))
+    _run(w)
+    expected = {"row_tn": (capi.ROUTE_TC_PAIR, capi.ROUTE_TC_PAIR_WIDE), "row_tn_e4m3": (capi.ROUTE_TC_PAIR, capi.ROUTE_TC_PAIR_WIDE),
+                "row_tn_f32": (capi.ROUTE_SIMT,)}.get(name, (capi.ROUTE_TC_256, capi.ROUTE_TC_128))
+    assert capi.last_route() in expected
+    _check_columns(w, [(0, 4), (2047, 2051), (4092, 4096)])
+
+
+def test_the_four_layouts_of_one_problem_agree():
+    """Same values stored in the four operand layouts: the outputs may differ by the order in which a tile's k-blocks
+    are added (one BF16 code, rarely), nothing more."""
+    import torch
+    from e5m2effma_b200 import workloads
+    dev = torch.device("cuda", 0)
+    outs = []
+    for name in ("row_tn", "row_nn", "row_nt", "row_tt"):
+        w = workloads.make(name, dev, 4)
+        _run(w)
+        outs.append(w.D.view(torch.int16).int())
+    for o in outs[1:]:
+        diff = (o - outs[0]).abs()
+        assert int(diff.max()) <= 1 and float((diff != 0).float().mean()) < 0.02
 
 
 def test_c5_adamw_sampled_chunks_bit_exact():

@@ -27,3 +27,13 @@ def test_strong_scaling_table():
     text = report.strong_table(d)
     assert "| headline | 340.0 us | 180.0 us, 93.0 % | 240.0 us, 70.0 % | unavailable |" in text
     assert "| wgrad | 2000.0 us | 1050.0 us, 96.0 % | - | - |" in text and "Weak scaling" in text
+
+
+def test_rows_table():
+    d = {"gemm_rows": [{"row": "e5ma_gemm NT E5M2 x E5M2 -> BF16", "ms_per_step": 0.06, "value": 2290.0, "unit": "TFLOP/s",
+                        "kernel": "tcgen05 one CTA, 256-row tiles", "peak": 3245.6, "peak_source": "measured: 2 x bf16_tflops burst",
+                        "frac": 0.7056, "clocks": {"sm_mhz": 1900}},
+                       {"row": "e5ma_gemm TN E5M2 x FP32 -> BF16", "error": "boom"}]}
+    text = report.rows_table(d)
+    assert "| e5ma_gemm NT E5M2 x E5M2 -> BF16 | 60.0 us | 2290 TFLOP/s | tcgen05 one CTA, 256-row tiles | 70.6 % of 3246 (measured: 2 x bf16_tflops burst) | 1900 |" in text
+    assert "failed: boom" in text
