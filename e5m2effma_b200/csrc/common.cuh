@@ -245,13 +245,14 @@ enum Opt {
   OPT_TC_SPLIT,       // E5MA_TC_SPLIT      0: the last round of tiles is not cut into slices
   OPT_TC_GRID,        // E5MA_TC_GRID       n: at most n CTAs in the one-CTA tensor-core kernel
   OPT_TC_WIDE,        // E5MA_TC_WIDE       0: no wide (256 x up to 512) pair tiles; n >= 256: that tile width
-  OPT_GEMV_KERNEL,    // E5MA_GEMV_KERNEL   0: register loads, 1: cp.async ring, 2: persistent bulk-copy ring
+  OPT_GEMV_KERNEL,    // E5MA_GEMV_KERNEL   0: register loads, 1: cp.async ring per warp, 2: persistent bulk-copy ring, 3: cp.async row streams per block
   OPT_GEMV_STAGES,    // E5MA_GEMV_STAGES   depth of the cp.async ring (2, 3, 4)
   OPT_GEMV_U,         // E5MA_GEMV_U        k-steps in flight per warp of the register-load kernel
   OPT_GEMV_MT,        // E5MA_GEMV_MT       2: 32 rows per block in the register-load kernel
   OPT_MIXED_PAIR,     // E5MA_MIXED_PAIR    0: FP8 x BF16 problems never take the CTA-pair kernel
   OPT_GEMV_KMAP,      // E5MA_GEMV_KMAP     1: each warp of the cp.async GEMV walks a contiguous eighth of K
   OPT_WIDEN_GROUPS,   // E5MA_WIDEN_GROUPS  1, 2: groups of warps that widen alternate k-blocks of a mixed FP8 x BF16 GEMM
+  OPT_GEMV_FMA_MAXN,  // E5MA_GEMV_FMA_MAXN 0..4: largest batch of FP8 / BF16 activations that takes the FP32-pipe GEMV kernel
   OPT_COUNT
 };
 int opt(Opt which);
@@ -264,7 +265,7 @@ int tuned_gemv(int key);
 
 // Which kernel the last e5ma_gemm call of this host thread launched (e5b_last_route()).
 enum Route { ROUTE_NONE = 0, ROUTE_GEMV = 1, ROUTE_GEMV_PERSISTENT = 2, ROUTE_TC_PAIR = 3, ROUTE_TC_PAIR_WIDE = 4,
-             ROUTE_TC_256 = 5, ROUTE_TC_128 = 6, ROUTE_SIMT = 7, ROUTE_TC_MIXED_PAIR = 8, ROUTE_GEMV_F32X = 9 };
+             ROUTE_TC_256 = 5, ROUTE_TC_128 = 6, ROUTE_SIMT = 7, ROUTE_TC_MIXED_PAIR = 8, ROUTE_GEMV_FMA = 9, ROUTE_GEMV_ROWS = 10 };
 void note_route(int r);
 // E5MA_OK and the properties of the current device when it is compute capability 10.x
 e5ma_status require_blackwell(const char *who, DeviceProps *out);

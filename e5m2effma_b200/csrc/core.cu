@@ -37,7 +37,8 @@ e5ma_status cuda_fail(cudaError_t e, const char *what) {
 // ---- switches and the route record ----------------------------------------------------------------
 static std::atomic<int> g_opt[OPT_COUNT];
 static const char *const kOptNames[OPT_COUNT] = {"FORCE_SIMT", "TC_PAIR", "TC_SPLIT", "TC_GRID", "TC_WIDE", "GEMV_KERNEL",
-                                                 "GEMV_STAGES", "GEMV_U", "GEMV_MT", "MIXED_PAIR", "GEMV_KMAP", "WIDEN_GROUPS"};
+                                                 "GEMV_STAGES", "GEMV_U", "GEMV_MT", "MIXED_PAIR", "GEMV_KMAP", "WIDEN_GROUPS",
+                                                 "GEMV_FMA_MAXN"};
 static void opt_init() {
   static std::once_flag once;
   std::call_once(once, [] {
@@ -60,9 +61,9 @@ int opt(Opt which) {
 // ---- tuned tables ---------------------------------------------------------------------------------
 struct TunedGemm { int eb, m, n, k, plan; };
 static const TunedGemm kTunedGemm[] = {E5B_TUNED_GEMM {0, 0, 0, 0, 0}};
-struct TunedFile { std::vector<TunedGemm> gemm; int gemv[3] = {TUNED_NONE, TUNED_NONE, TUNED_NONE}; };
+struct TunedFile { std::vector<TunedGemm> gemm; int gemv[4] = {TUNED_NONE, TUNED_NONE, TUNED_NONE, TUNED_NONE}; };
 
-// Text table: one entry per line, `gemm <elem bytes> <m> <n> <k> <plan>` or `gemv kernel|stages|kmap <value>`;
+// Text table: one entry per line, `gemm <elem bytes> <m> <n> <k> <plan>` or `gemv kernel|stages|kmap|fma_maxn <value>`;
 // anything else (comments, blank lines) is skipped.
 static const TunedFile &tuned_file() {
   static TunedFile tf;
@@ -81,6 +82,7 @@ static const TunedFile &tuned_file() {
         if (!strcmp(key, "kernel")) tf.gemv[0] = v;
         else if (!strcmp(key, "stages")) tf.gemv[1] = v;
         else if (!strcmp(key, "kmap")) tf.gemv[2] = v;
+        else if (!strcmp(key, "fma_maxn")) tf.gemv[3] = v;
       }
     }
     fclose(f);
@@ -95,9 +97,9 @@ int tuned_gemm_plan(int elem_bytes, int m, int n, int k) {
   return TUNED_NONE;
 }
 int tuned_gemv(int key) {
-  if (key < 0 || key > 2) return TUNED_NONE;
+  if (key < 0 || key > 3) return TUNED_NONE;
   if (tuned_file().gemv[key] != TUNED_NONE) return tuned_file().gemv[key];
-  const int compiled[3] = {E5B_TUNED_GEMV_KERNEL, E5B_TUNED_GEMV_STAGES, E5B_TUNED_GEMV_KMAP};
+  const int compiled[4] = {E5B_TUNED_GEMV_KERNEL, E5B_TUNED_GEMV_STAGES, E5B_TUNED_GEMV_KMAP, E5B_TUNED_GEMV_FMA_MAXN};
   return compiled[key];
 }
 

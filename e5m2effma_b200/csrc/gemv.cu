@@ -269,20 +269,146 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_async_kernel(const uint8_t
   if (o.amax) block_amax(o.amax, mx);
 }
 
-// ---- FP32 activations: the same stream on the FP32 pipe ------------------------------------------
-// An FP32 X does not fit a tensor-core operand without splitting it, and the reference sends this case to its
-// bandwidth kernel like every other skinny problem with FP8 weights (src/gemm_e5m2effma.cu:100-102), where each
-// product is one FP32 FMA (src/gemv_e5m2effma.cuh:27-79).  So does this kernel: a block owns 16 rows; a warp
-// owns R of them over 1 / KS of K and walks it 512 bytes at a time (16 bytes per lane and row, the next step's
-// loads issued before this step's arithmetic); every lane keeps R x NC running sums of its own k positions (one
-// FMA per product, exact decode of W), a butterfly adds the lanes, the KS parts meet in shared memory in a fixed
-// order and 128 threads run the common epilogue.  NC = n rounded up to 1, 2, 4, 8 sizes the register tile.
-template <int AT, int NC, int R>
-__global__ void __launch_bounds__(GV_WARPS * 32) gemv_f32x_kernel(const uint8_t *__restrict__ W, int lda,
-                                                                  const float *__restrict__ X, int ldx, int m, int n, int k,
-                                                                  OutDesc o) {
+// ---- tensor-core kernel with row streams -------------------------------------------------------------
+// The arithmetic of gemv_async_kernel behind the access pattern of the FP32-pipe kernel below: the block's eight
+// warps copy a stage of 16 rows x 512 bytes together, warp w rows 2w and 2w + 1 with one cp.async instruction per
+// row (512 contiguous bytes per instruction, every row a sequential stream), S stages ahead; a stage that has landed
+// is consumed by all warps, warp w taking bytes [64 w, 64 w + 64) of each row as two of the 16-byte fragments above.
+// One block barrier per stage makes the copies of all warps visible and frees the slot consumed before it.  Rows
+// are 576 bytes apart in shared memory, so the 16-byte reads of a quarter warp (two rows x four k-chunks) hit
+// distinct banks.
+constexpr int GR_PITCH = 512 + 64, GR_STAGE = 16 * GR_PITCH;
+
+template <int AT, int XT, int S>
+__global__ void __launch_bounds__(GV_WARPS * 32) gemv_rows_kernel(const uint8_t *__restrict__ W, int lda,
+                                                                  const uint8_t *__restrict__ X, int ldx, int m, int n,
+                                                                  int k, OutDesc o) {
+  extern __shared__ __align__(16) uint8_t ring_raw[];        // [stage][row 0..15][576 bytes]
+  __shared__ float red[GV_WARPS][16][9];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * 16;
+  constexpr int XB = XT == E5MA_BF16 ? 2 : 1;
+  constexpr int XW = XT == E5MA_BF16 ? 2 : 1;
+  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring_raw);
+
+  // copies: rows 2 warp and 2 warp + 1, bytes [16 lane, 16 lane + 16) of the stage
+  const int ca = row0 + 2 * warp, cb = ca + 1;
+  const bool la = ca < m, lb = cb < m;
+  const uint8_t *wa = W + (size_t)(la ? ca : 0) * lda + lane * 16, *wb = W + (size_t)(lb ? cb : 0) * lda + lane * 16;
+  const uint32_t dst0 = ring_s + (uint32_t)(2 * warp) * GR_PITCH + lane * 16;
+  const int stages = (k + 511) / 512;
+  const auto issue = [&](int it) {
+    if (it < stages) {
+      const int kc = it * 512;
+      const bool in = kc + lane * 16 < k;
+      const uint32_t dst = dst0 + (uint32_t)(it % S) * GR_STAGE;
+      cp_async16(dst, wa + kc, la && in, false);
+      cp_async16(dst + GR_PITCH, wb + kc, lb && in, false);
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int it = 0; it < S - 1; ++it) issue(it);
+
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint8_t *xcol = X + (size_t)g * ldx * XB;
+  const bool xlive = g < n;
+  const int koff = warp * 64 + t * 16;           // this lane's 16 k positions inside a stage
+  const auto load_x = [&](int it, uint4 (&xq)[XW]) {
+    const int kk = it * 512 + koff;
+#pragma unroll
+    for (int q = 0; q < XW; ++q)
+      xq[q] = xlive && kk < k ? __ldg(reinterpret_cast<const uint4 *>(xcol + (size_t)kk * XB) + q) : make_uint4(0, 0, 0, 0);
+  };
+  uint4 xq[XW], xn[XW];
+  load_x(0, xq);
+  const uint8_t *frag = ring_raw + (size_t)g * GR_PITCH + koff;
+  for (int it = 0; it < stages; ++it) {
+    cp_async_wait<S - 2>();           // this thread's copies of stage `it` have landed ...
+    __syncthreads();                  // ... everybody's have, and everybody is done with stage it - 1
+    issue(it + S - 1);                // refills the slot of stage it - 1
+    load_x(it + 1, xn);
+    const uint8_t *slot = frag + (size_t)(it % S) * GR_STAGE;
+    const uint4 wq0 = *reinterpret_cast<const uint4 *>(slot);
+    const uint4 wq1 = *reinterpret_cast<const uint4 *>(slot + 8 * GR_PITCH);
+    uint32_t xw[8];
+    if (XT == E5MA_BF16) {
+      xw[0] = xq[0].x; xw[1] = xq[0].y; xw[2] = xq[0].z; xw[3] = xq[0].w;
+      xw[4] = xq[XW - 1].x; xw[5] = xq[XW - 1].y; xw[6] = xq[XW - 1].z; xw[7] = xq[XW - 1].w;
+    } else {
+      const uint32_t q[4] = {xq[0].x, xq[0].y, xq[0].z, xq[0].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) fp8x4_to_bf16x2<XT == E5MA_BF16 ? E5MA_E5M2 : XT>(q[e], xw[2 * e], xw[2 * e + 1]);
+    }
+    const uint32_t qa[4] = {wq0.x, wq0.y, wq0.z, wq0.w};
+    const uint32_t qb[4] = {wq1.x, wq1.y, wq1.z, wq1.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      uint32_t a0, a2, a1, a3;
+      fp8x4_to_bf16x2<AT>(qa[e], a0, a2);   // row g:   k pairs (0,1) and (2,3) of this word
+      fp8x4_to_bf16x2<AT>(qb[e], a1, a3);   // row g+8
+      mma_bf16_16816((e & 1) ? acc2 : acc, a0, a1, a2, a3, xw[2 * e], xw[2 * e + 1]);
+    }
+#pragma unroll
+    for (int q = 0; q < XW; ++q) xq[q] = xn[q];
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) acc[e] = __fadd_rn(acc[e], acc2[e]);
+  cp_async_wait<0>();
+
+  red[warp][g][2 * t] = acc[0];
+  red[warp][g][2 * t + 1] = acc[1];
+  red[warp][g + 8][2 * t] = acc[2];
+  red[warp][g + 8][2 * t + 1] = acc[3];
+  __syncthreads();
+  const OutScalars r = out_begin(o);
+  float mx = 0.f;
+  if (threadIdx.x < 128) {
+    const int il = threadIdx.x & 15, j = threadIdx.x >> 4, i = row0 + il;
+    if (i < m && j < n) {
+      float s = red[0][il][j];
+#pragma unroll
+      for (int w = 1; w < GV_WARPS; ++w) s = __fadd_rn(s, red[w][il][j]);
+      mx = out_store(o, r, i, j, s);
+    }
+  }
+  if (o.amax) block_amax(o.amax, mx);
+}
+
+// ---- the same stream on the FP32 pipe: long contiguous reads, one FMA per product ------------------------
+// A warp owns R whole rows (over 1 / KS of K) and walks them 512 bytes at a time: 16 bytes per lane and row, so
+// one load instruction of a warp covers 512 contiguous bytes of one row and a row is read front to back by the
+// same warp -- the access pattern DRAM likes best (measured on 8192 x 8192 weights, batch 1: 14.7 us against
+// 16.1 us for the tensor-core kernel above, whose warps gather 16 rows x 128 bytes per step).  The price is the
+// arithmetic: every lane keeps R x NC running sums of its own k positions and spends one FP32 FMA per product, as
+// the reference's gemv_kernel does (src/gemv_e5m2effma.cuh:27-79), so the kernel only pays for small n -- and for
+// FP32 activations, which do not fit a tensor-core operand without splitting them and which the reference routes
+// here like every other skinny problem with FP8 weights (src/gemm_e5m2effma.cu:100-102).
+// W is decoded exactly; X of any operand dtype becomes FP32 exactly; a butterfly adds the lanes, the KS parts meet
+// in shared memory in a fixed order and 128 threads run the common epilogue.  NC = n rounded up to 1, 2, 4, 8.
+
+// four consecutive X values of column storage `col` (XT elements) starting at element k0 -> FP32
+template <int XT>
+__device__ __forceinline__ void load_x4(const uint8_t *col, int k0, float x[4]) {
+  if (XT == E5MA_FP32) {
+    const float4 v = __ldg(reinterpret_cast<const float4 *>(col) + (k0 >> 2));
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+  } else if (XT == E5MA_BF16) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2 *>(col) + (k0 >> 2));
+    x[0] = __uint_as_float(v.x << 16); x[1] = __uint_as_float(v.x & 0xFFFF0000u);
+    x[2] = __uint_as_float(v.y << 16); x[3] = __uint_as_float(v.y & 0xFFFF0000u);
+  } else {
+    fp8x4_to_f32<XT == E5MA_E4M3 ? E5MA_E4M3 : E5MA_E5M2>(__ldg(reinterpret_cast<const uint32_t *>(col) + (k0 >> 2)), x);
+  }
+}
+
+template <int AT, int XT, int NC, int R>
+__global__ void __launch_bounds__(GV_WARPS * 32) gemv_fma_kernel(const uint8_t *__restrict__ W, int lda,
+                                                                 const uint8_t *__restrict__ X, int ldx, int m, int n, int k,
+                                                                 OutDesc o) {
   constexpr int GROUPS = 16 / R, KS = GV_WARPS / GROUPS;
   __shared__ float red[KS][16][9];
+  constexpr int XB = XT == E5MA_FP32 ? 4 : (XT == E5MA_BF16 ? 2 : 1);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int grp = warp % GROUPS, ks = warp / GROUPS;
   const int row0 = blockIdx.x * 16 + grp * R;
@@ -313,7 +439,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_f32x_kernel(const uint8_t 
     load_w(nxt, k0 + 512);
     const bool in = k0 < kend;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {          // one 32-bit word of every row: four codes against four floats of every column
+    for (int q = 0; q < 4; ++q) {          // one 32-bit word of every row: four codes against four values of every column
       float wf[R][4];
 #pragma unroll
       for (int r = 0; r < R; ++r) {
@@ -322,14 +448,12 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_f32x_kernel(const uint8_t 
       }
 #pragma unroll
       for (int j = 0; j < NC; ++j) {
-        const float4 x = in && j < n ? __ldg(reinterpret_cast<const float4 *>(X + (size_t)j * ldx + k0 + 4 * q)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        if (in && j < n) load_x4<XT>(X + (size_t)j * ldx * XB, k0 + 4 * q, x);
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          acc[r][j] = __fmaf_rn(wf[r][0], x.x, acc[r][j]);
-          acc[r][j] = __fmaf_rn(wf[r][1], x.y, acc[r][j]);
-          acc[r][j] = __fmaf_rn(wf[r][2], x.z, acc[r][j]);
-          acc[r][j] = __fmaf_rn(wf[r][3], x.w, acc[r][j]);
-        }
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[r][j] = __fmaf_rn(wf[r][e], x[e], acc[r][j]);
       }
     }
 #pragma unroll
@@ -360,16 +484,119 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_f32x_kernel(const uint8_t 
   if (o.amax) block_amax(o.amax, mx);
 }
 
-template <int AT>
-static cudaError_t gemv_f32x(const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k, const OutDesc &o,
-                             cudaStream_t s) {
+// Wider batches on the FP32 pipe (FP32 activations only: the others have the tensor-core kernel).  Reading X per lane
+// straight from L1 / L2 as above costs NC loads per four codes and drowns the weight stream (8192 x 8192, n = 8:
+// 183 us).  Here every warp of the block owns two rows over all of K, so that all warps need the same 512 k
+// positions of X at the same time: the block stages them in shared memory once per step (double-buffered, laid out
+// [group of four k][lane] so that the lanes' 16-byte reads are conflict-free) and a lane reads them from there.
+template <int AT, int NC>
+__global__ void __launch_bounds__(GV_WARPS * 32) gemv_fma_staged_kernel(const uint8_t *__restrict__ W, int lda,
+                                                                        const float *__restrict__ X, int ldx, int m, int n,
+                                                                        int k, OutDesc o) {
+  constexpr int R = 2;
+  __shared__ __align__(16) float xs[2][NC][512];
+  __shared__ float red[16][9];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int row0 = blockIdx.x * 16 + warp * R;
+  const uint8_t *wrow[R];
+  bool live[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    live[r] = row0 + r < m;
+    wrow[r] = W + (size_t)(live[r] ? row0 + r : 0) * lda;
+  }
+  float acc[R][NC];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int j = 0; j < NC; ++j) acc[r][j] = 0.f;
+
+  // X[j][kb + 4c .. 4c + 4) -> xs[buf][j][((c & 3) * 32 + (c >> 2)) * 4 ..]: c >> 2 is the lane that owns these k
+  const auto stage = [&](int buf, int kb) {
+    for (int idx = threadIdx.x; idx < NC * 128; idx += GV_WARPS * 32) {
+      const int j = idx >> 7, c = idx & 127, kk = kb + 4 * c;
+      const float4 v = j < n && kk < k ? __ldg(reinterpret_cast<const float4 *>(X + (size_t)j * ldx + kk)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4 *>(&xs[buf][j][((c & 3) * 32 + (c >> 2)) * 4]) = v;
+    }
+  };
+  uint4 cur[R], nxt[R];
+  const auto load_w = [&](uint4 (&q)[R], int k0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) q[r] = live[r] && k0 < k ? ld_stream16(wrow[r] + k0) : make_uint4(0, 0, 0, 0);
+  };
+  load_w(cur, lane * 16);
+  stage(0, 0);
+  __syncthreads();
+  int buf = 0;
+  for (int kb = 0; kb < k; kb += 512, buf ^= 1) {
+    load_w(nxt, kb + 512 + lane * 16);
+    if (kb + 512 < k) stage(buf ^ 1, kb + 512);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float wf[R][4];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const uint32_t word = q == 0 ? cur[r].x : q == 1 ? cur[r].y : q == 2 ? cur[r].z : cur[r].w;
+        fp8x4_to_f32<AT>(word, wf[r]);
+      }
+#pragma unroll
+      for (int j = 0; j < NC; ++j) {
+        const float4 x = *reinterpret_cast<const float4 *>(&xs[buf][j][(q * 32 + lane) * 4]);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          acc[r][j] = __fmaf_rn(wf[r][0], x.x, acc[r][j]);
+          acc[r][j] = __fmaf_rn(wf[r][1], x.y, acc[r][j]);
+          acc[r][j] = __fmaf_rn(wf[r][2], x.z, acc[r][j]);
+          acc[r][j] = __fmaf_rn(wf[r][3], x.w, acc[r][j]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) cur[r] = nxt[r];
+    __syncthreads();     // the other buffer is complete; this one may be overwritten by the next step's staging
+  }
+
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      float v = acc[r][j];
+#pragma unroll
+      for (int d = 16; d; d >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xFFFFFFFFu, v, d));
+      if (lane == r * NC + j) red[warp * R + r][j] = v;
+    }
+  __syncthreads();
+  const OutScalars sc = out_begin(o);
+  float mx = 0.f;
+  if (threadIdx.x < 128) {
+    const int il = threadIdx.x & 15, j = threadIdx.x >> 4, i = blockIdx.x * 16 + il;
+    if (i < m && j < n) mx = out_store(o, sc, i, j, red[il][j]);
+  }
+  if (o.amax) block_amax(o.amax, mx);
+}
+
+template <int AT, int XT>
+static cudaError_t gemv_fma_x(const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k, const OutDesc &o,
+                              cudaStream_t s) {
   const unsigned grid = (unsigned)((m + 15) / 16);
-  const float *x = reinterpret_cast<const float *>(X);
-  if (n == 1) gemv_f32x_kernel<AT, 1, 4><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, x, ldx, m, n, k, o);
-  else if (n == 2) gemv_f32x_kernel<AT, 2, 4><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, x, ldx, m, n, k, o);
-  else if (n <= 4) gemv_f32x_kernel<AT, 4, 2><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, x, ldx, m, n, k, o);
-  else gemv_f32x_kernel<AT, 8, 2><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, x, ldx, m, n, k, o);
+  if (n == 1) gemv_fma_kernel<AT, XT, 1, 4><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, X, ldx, m, n, k, o);
+  else if (n == 2) gemv_fma_kernel<AT, XT, 2, 4><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, X, ldx, m, n, k, o);
+  else if (XT == E5MA_FP32 && n <= 4) gemv_fma_staged_kernel<AT, 4><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, reinterpret_cast<const float *>(X), ldx, m, n, k, o);
+  else if (XT == E5MA_FP32) gemv_fma_staged_kernel<AT, 8><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, reinterpret_cast<const float *>(X), ldx, m, n, k, o);
+  else if (n <= 4) gemv_fma_kernel<AT, XT, 4, 2><<<grid, GV_WARPS * 32, 0, s>>>(A, lda, X, ldx, m, n, k, o);
+  else return cudaErrorNotSupported;
   return cudaGetLastError();
+}
+template <int AT>
+static cudaError_t gemv_fma(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
+                            const OutDesc &o, cudaStream_t s) {
+  switch (x_dtype) {
+    case E5MA_FP32: return gemv_fma_x<AT, E5MA_FP32>(A, lda, X, ldx, m, n, k, o, s);
+    case E5MA_BF16: return gemv_fma_x<AT, E5MA_BF16>(A, lda, X, ldx, m, n, k, o, s);
+    case E5MA_E5M2: return gemv_fma_x<AT, E5MA_E5M2>(A, lda, X, ldx, m, n, k, o, s);
+    case E5MA_E4M3: return gemv_fma_x<AT, E5MA_E4M3>(A, lda, X, ldx, m, n, k, o, s);
+    default: return cudaErrorNotSupported;
+  }
 }
 
 // ---- persistent kernel with a bulk-copy weight ring ------------------------------------------------
@@ -654,6 +881,27 @@ unsigned int gemv_fault_read_and_clear() {
   return v;
 }
 
+template <int AT, int S>
+static cudaError_t gemv_rows_x(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
+                               const OutDesc &o, cudaStream_t s) {
+  constexpr int SMEM = S * GR_STAGE;
+  const unsigned grid = (unsigned)((m + 15) / 16);
+#define E5B_GEMV_ROWS(XT)                                                                                  \
+  {                                                                                                        \
+    static SmemOptIn optin;                                                                                \
+    if (const cudaError_t e = optin.ensure(gemv_rows_kernel<AT, XT, S>, SMEM)) return e;                   \
+    gemv_rows_kernel<AT, XT, S><<<grid, GV_WARPS * 32, SMEM, s>>>(A, lda, X, ldx, m, n, k, o);             \
+  }
+  switch (x_dtype) {
+    case E5MA_BF16: E5B_GEMV_ROWS(E5MA_BF16) break;
+    case E5MA_E5M2: E5B_GEMV_ROWS(E5MA_E5M2) break;
+    case E5MA_E4M3: E5B_GEMV_ROWS(E5MA_E4M3) break;
+    default: return cudaErrorNotSupported;
+  }
+#undef E5B_GEMV_ROWS
+  return cudaGetLastError();
+}
+
 template <int AT, int GA_STAGES>
 static cudaError_t gemv_async_x(int x_dtype, const uint8_t *A, int lda, const uint8_t *X, int ldx, int m, int n, int k,
                                 const OutDesc &o, cudaStream_t s) {
@@ -710,10 +958,13 @@ cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda,
   // Persistent bulk-copy kernel: only on request (switch GEMV_KERNEL = 2) and when X fits beside a ring of at
   // least three stages.  Measured on B200 (8192 x 8192 weights): 24 us against 15.6 us for the cp.async kernel --
   // bulk copies keep too few bytes in flight per SM, whatever their size.
-  if (x_dtype == E5MA_FP32) {
-    note_route(ROUTE_GEMV_F32X);
-    if (a_dtype == E5MA_E5M2) return gemv_f32x<E5MA_E5M2>(A, lda, X, ldx, m, n, k, o, s);
-    if (a_dtype == E5MA_E4M3) return gemv_f32x<E5MA_E4M3>(A, lda, X, ldx, m, n, k, o, s);
+  // FP32 activations always, other activations up to the tuned batch size (switch GEMV_FMA_MAXN): the FP32-pipe kernel
+  // (a request for a particular tensor-core kernel, switch GEMV_KERNEL, keeps them off it unless GEMV_FMA_MAXN is set too)
+  const int fma_maxn = opt(OPT_GEMV_FMA_MAXN) >= 0 ? opt(OPT_GEMV_FMA_MAXN) : (opt(OPT_GEMV_KERNEL) >= 0 ? 0 : tuned_gemv(3));
+  if (x_dtype == E5MA_FP32 || n <= (fma_maxn < 4 ? fma_maxn : 4)) {
+    note_route(ROUTE_GEMV_FMA);
+    if (a_dtype == E5MA_E5M2) return gemv_fma<E5MA_E5M2>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
+    if (a_dtype == E5MA_E4M3) return gemv_fma<E5MA_E4M3>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
     return cudaErrorNotSupported;
   }
   const int which = opt(OPT_GEMV_KERNEL) >= 0 ? opt(OPT_GEMV_KERNEL) : tuned_gemv(0);
@@ -724,8 +975,17 @@ cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda,
     if (a_dtype == E5MA_E4M3) return gemv_bulk_x<E5MA_E4M3>(x_dtype, A, lda, X, ldx, m, n, k, o, sms, bp, s);
     return cudaErrorNotSupported;
   }
-  const bool use_async = which != 0;
   note_route(ROUTE_GEMV);
+  if (which == 3) {     // row streams: ring depth 3 or 4
+    note_route(ROUTE_GEMV_ROWS);
+    const int depth = (opt(OPT_GEMV_STAGES) > 0 ? opt(OPT_GEMV_STAGES) : tuned_gemv(1)) == 3 ? 3 : 4;
+    if (a_dtype == E5MA_E5M2)
+      return depth == 3 ? gemv_rows_x<E5MA_E5M2, 3>(x_dtype, A, lda, X, ldx, m, n, k, o, s) : gemv_rows_x<E5MA_E5M2, 4>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
+    if (a_dtype == E5MA_E4M3)
+      return depth == 3 ? gemv_rows_x<E5MA_E4M3, 3>(x_dtype, A, lda, X, ldx, m, n, k, o, s) : gemv_rows_x<E5MA_E4M3, 4>(x_dtype, A, lda, X, ldx, m, n, k, o, s);
+    return cudaErrorNotSupported;
+  }
+  const bool use_async = which != 0;
   if (use_async) {
     int stages = tuned_gemv(1);   // 2 = 32 KiB per block: every row tile of an 8192-row matrix is resident in one wave
     if (opt(OPT_GEMV_STAGES) > 0) stages = opt(OPT_GEMV_STAGES);

@@ -45,7 +45,7 @@ def test_gemv_route_within_tolerance(case):
     from e5m2effma_b200 import capi
     d = GemmData(case)
     got, amax = d.run_gpu()
-    assert capi.last_route() == (capi.ROUTE_GEMV_F32X if case.bt == FP32 else capi.ROUTE_GEMV)
+    assert capi.last_route() in ((capi.ROUTE_GEMV_FMA,) if case.bt == FP32 else (capi.ROUTE_GEMV, capi.ROUTE_GEMV_FMA, capi.ROUTE_GEMV_ROWS))
     check_tolerance(d, got, amax)
 
 
@@ -131,22 +131,34 @@ def test_runs_are_deterministic():
     assert np.array_equal(a, b) and am_a == am_b
 
 
-@pytest.mark.parametrize("kmap", [0, 1])
+GEMV_VARIANTS = {"async ring, interleaved k": {"GEMV_KERNEL": 1, "GEMV_KMAP": 0}, "async ring, contiguous k": {"GEMV_KERNEL": 1, "GEMV_KMAP": 1},
+                 "register loads": {"GEMV_KERNEL": 0}, "row streams, 4 stages": {"GEMV_KERNEL": 3}, "row streams, 3 stages": {"GEMV_KERNEL": 3, "GEMV_STAGES": 3},
+                 "FP32 pipe": {"GEMV_FMA_MAXN": 4}}
+
+
+@pytest.mark.parametrize("variant", list(GEMV_VARIANTS))
 @pytest.mark.parametrize("case", GEMV_CASES[::5] + [GemmCase(1, 0, 2048, 8, 2064, E5M2, BF16, BF16, BF16, -1, 1.0, 0.0, vec=1, seed=33, tight=True),
-                                                    GemmCase(1, 0, 1000, 3, 4112, E4M3, E5M2, FP32, -1, BF16, 1.0, 1.0, vec=3, seed=34)],
+                                                    GemmCase(1, 0, 1000, 3, 4112, E4M3, E5M2, FP32, -1, BF16, 1.0, 1.0, vec=3, seed=34),
+                                                    GemmCase(1, 0, 531, 2, 1552, E5M2, BF16, BF16, -1, BF16, 1.0, 0.0, vec=1, seed=35),
+                                                    GemmCase(1, 0, 77, 4, 528, E4M3, E4M3, FP32, FP32, -1, 0.5, 1.0, vec=3, seed=36)],
                          ids=lambda c: c.label())
-def test_gemv_k_mappings_within_tolerance(case, kmap):
-    """The cp.async GEMV with interleaved 128-byte k-steps (0) and with each warp on a contiguous eighth of K (1, the
-    tuned default): same results within the bound."""
+def test_gemv_kernel_variants_within_tolerance(case, variant):
+    """Every GEMV kernel the switches can select -- the cp.async ring with interleaved 128-byte k-steps and with each
+    warp on a contiguous eighth of K, register loads, the row-stream ring at both depths, the FP32-pipe kernel for
+    batches up to 4 -- gives results within the bound."""
     from e5m2effma_b200 import capi
     if case.bt == FP32:
-        pytest.skip("FP32 x runs the CUDA-core kernel")
-    capi.set_option("GEMV_KMAP", kmap)
+        pytest.skip("FP32 x has one kernel (covered by the case matrix above)")
+    opts = GEMV_VARIANTS[variant]
+    for name, v in opts.items():
+        capi.set_option(name, v)
     try:
         d = GemmData(case)
         got, amax = d.run_gpu()
         route = capi.last_route()
     finally:
-        capi.set_option("GEMV_KMAP", None)
+        for name in opts:
+            capi.set_option(name, None)
     check_tolerance(d, got, amax)
-    assert route == capi.ROUTE_GEMV
+    assert route == (capi.ROUTE_GEMV_FMA if variant == "FP32 pipe" and case.n <= 4 else
+                     capi.ROUTE_GEMV_ROWS if variant.startswith("row streams") else capi.ROUTE_GEMV)
