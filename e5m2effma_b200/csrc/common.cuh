@@ -253,6 +253,7 @@ enum Opt {
   OPT_GEMV_KMAP,      // E5MA_GEMV_KMAP     1: each warp of the cp.async GEMV walks a contiguous eighth of K
   OPT_WIDEN_GROUPS,   // E5MA_WIDEN_GROUPS  1, 2: groups of warps that widen alternate k-blocks of a mixed FP8 x BF16 GEMM
   OPT_GEMV_FMA_MAXN,  // E5MA_GEMV_FMA_MAXN 0..4: largest batch of FP8 / BF16 activations that takes the FP32-pipe GEMV kernel
+  OPT_GEMV_F16,       // E5MA_GEMV_F16      0: the cp.async GEMV never uses FP16 arithmetic (BF16 everywhere, as gemv_async_kernel)
   OPT_COUNT
 };
 int opt(Opt which);

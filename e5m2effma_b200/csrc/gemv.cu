@@ -840,6 +840,185 @@ __global__ void __launch_bounds__(GB_THREADS, 1) gemv_bulk_kernel(const uint8_t 
   else __syncthreads();
 }
 
+// ---- the cp.async ring with FP16 arithmetic ---------------------------------------------------------
+// gemv_async_kernel is bound by its instruction stream, and half of that stream widens W to BF16 (two converter
+// instructions and half a byte permute per pair of codes; with FP8 activations, whose widening comes on top, the
+// same weights take 18.1 us instead of 15.9 us).  To FP16 the widening is one instruction per pair: E5M2 is the
+// upper byte of an FP16, E4M3 has a hardware converter.  Products of an FP8 and an FP16 value are exact in the
+// FP32 accumulator, the sums are the same FP32 sums, so the result does not change -- provided X is FP16.  FP8
+// activations always convert exactly (on the fly, same single instruction per pair).  BF16 activations are
+// converted once per block into shared memory behind the ring (n columns of k FP16 values; the launcher offers
+// this kernel only when that fits) and every value is checked on the way: if one does not survive the round trip
+// (|x| >= 65520, or bits below 2^-24), the block runs the BF16 arithmetic of gemv_async_kernel instead.  Both
+// paths add the same exact products in the same order.
+template <int GA_STAGES>
+struct GaRing {
+  uint8_t *my_ring;
+  uint32_t my_ring_s;
+  const uint8_t *wa, *wb;
+  bool la, lb;
+  int k, kmap, warp, per_warp, steps, t;
+  __device__ __forceinline__ int kstart(int it) const { return (kmap ? warp * per_warp + it : warp + GV_WARPS * it) * 128; }
+  __device__ __forceinline__ void issue(int it) const {
+    if (it < steps) {
+      const int kc = kstart(it) + t * 16;
+      const uint32_t dst = my_ring_s + (uint32_t)(it % GA_STAGES) * 2048;
+      const bool wide = kmap != 0;
+      cp_async16(dst, wa + kc, la && kc < k, wide);
+      cp_async16(dst + 512, wb + kc, lb && kc < k, wide);
+      cp_async16(dst + 1024, wa + kc + 64, la && kc + 64 < k, wide);
+      cp_async16(dst + 1536, wb + kc + 64, lb && kc + 64 < k, wide);
+    }
+    cp_async_commit();
+  }
+};
+
+// MODE 0: BF16 arithmetic, X (XT) from global memory.  MODE 1: FP16 arithmetic, FP8 X from global memory.
+// MODE 2: FP16 arithmetic, X as FP16 in shared memory (xcol then points there).
+template <int AT, int XT, int GA_STAGES, int MODE>
+__device__ __forceinline__ void ga_mainloop(const GaRing<GA_STAGES> &rg, const uint8_t *xcol, bool xlive, float (&acc)[4],
+                                            float (&acc2)[4]) {
+  constexpr int XB = MODE == 2 ? 2 : (XT == E5MA_BF16 ? 2 : 1);
+  constexpr int XW = XB;                        // 16-byte loads of X per 16 elements
+  const int k = rg.k, t = rg.t;
+  const auto load_x = [&](int it, uint4 (&xq)[2][XW]) {
+    const int kc = rg.kstart(it);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int kk = kc + h * 64 + t * 16;
+#pragma unroll
+      for (int q = 0; q < XW; ++q) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(xcol + (size_t)kk * XB) + q;
+        xq[h][q] = xlive && kk < k ? (MODE == 2 ? *src : __ldg(src)) : make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  uint4 xq[2][XW], xn[2][XW];
+  if (MODE != 2) load_x(0, xq);
+  for (int it = 0; it < rg.steps; ++it) {
+    rg.issue(it + GA_STAGES - 1);
+    if (MODE != 2) load_x(it + 1, xn);   // X of the next step is fetched while this one is consumed (zeros beyond k)
+    else load_x(it, xq);                 // shared memory: no need to look ahead
+    cp_async_wait<GA_STAGES - 1>();
+    const uint8_t *slot = rg.my_ring + (size_t)(it % GA_STAGES) * 2048;
+    uint4 wq[2][2];
+    wq[0][0] = *reinterpret_cast<const uint4 *>(slot);
+    wq[0][1] = *reinterpret_cast<const uint4 *>(slot + 512);
+    wq[1][0] = *reinterpret_cast<const uint4 *>(slot + 1024);
+    wq[1][1] = *reinterpret_cast<const uint4 *>(slot + 1536);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t xw[8];
+      if (XW == 2) {
+        xw[0] = xq[h][0].x; xw[1] = xq[h][0].y; xw[2] = xq[h][0].z; xw[3] = xq[h][0].w;
+        xw[4] = xq[h][XW - 1].x; xw[5] = xq[h][XW - 1].y; xw[6] = xq[h][XW - 1].z; xw[7] = xq[h][XW - 1].w;
+      } else {
+        const uint32_t q[4] = {xq[h][0].x, xq[h][0].y, xq[h][0].z, xq[h][0].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (MODE == 0) fp8x4_to_bf16x2<XT == E5MA_BF16 ? E5MA_E5M2 : XT>(q[e], xw[2 * e], xw[2 * e + 1]);
+          else fp8x4_to_f16x2<XT == E5MA_BF16 ? E5MA_E5M2 : XT>(q[e], xw[2 * e], xw[2 * e + 1]);
+        }
+      }
+      const uint32_t qa[4] = {wq[h][0].x, wq[h][0].y, wq[h][0].z, wq[h][0].w};
+      const uint32_t qb[4] = {wq[h][1].x, wq[h][1].y, wq[h][1].z, wq[h][1].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        uint32_t a0, a2, a1, a3;
+        if (MODE == 0) {
+          fp8x4_to_bf16x2<AT>(qa[e], a0, a2);   // row g:   k pairs (0,1) and (2,3) of this word
+          fp8x4_to_bf16x2<AT>(qb[e], a1, a3);   // row g+8
+          mma_bf16_16816((e & 1) ? acc2 : acc, a0, a1, a2, a3, xw[2 * e], xw[2 * e + 1]);
+        } else {
+          fp8x4_to_f16x2<AT>(qa[e], a0, a2);
+          fp8x4_to_f16x2<AT>(qb[e], a1, a3);
+          mma_f16_16816((e & 1) ? acc2 : acc, a0, a1, a2, a3, xw[2 * e], xw[2 * e + 1]);
+        }
+      }
+    }
+    if (MODE != 2) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int q = 0; q < XW; ++q) xq[h][q] = xn[h][q];
+    }
+  }
+}
+
+template <int AT, int XT, int GA_STAGES>
+__global__ void __launch_bounds__(GV_WARPS * 32) gemv_async16_kernel(const uint8_t *__restrict__ W, int lda,
+                                                                     const uint8_t *__restrict__ X, int ldx, int m, int n,
+                                                                     int k, int kmap, int x_pitch, OutDesc o) {
+  extern __shared__ __align__(16) uint8_t ring_raw[];        // the ring as in gemv_async_kernel, then (BF16 X) n x x_pitch bytes of FP16
+  __shared__ float red[GV_WARPS][16][9];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * 16;
+  GaRing<GA_STAGES> rg;
+  rg.my_ring = ring_raw + (size_t)warp * GA_STAGES * 2048 + lane * 16;
+  rg.my_ring_s = (uint32_t)__cvta_generic_to_shared(rg.my_ring);
+  const int ra = row0 + g, rb = ra + 8;
+  rg.la = ra < m;
+  rg.lb = rb < m;
+  rg.wa = W + (size_t)(rg.la ? ra : 0) * lda;
+  rg.wb = W + (size_t)(rg.lb ? rb : 0) * lda;
+  const int kblocks = (k + 127) / 128;
+  rg.per_warp = (kblocks + GV_WARPS - 1) / GV_WARPS;
+  rg.k = k; rg.kmap = kmap; rg.warp = warp; rg.t = t;
+  rg.steps = kmap ? (kblocks - warp * rg.per_warp < rg.per_warp ? (kblocks > warp * rg.per_warp ? kblocks - warp * rg.per_warp : 0) : rg.per_warp)
+                  : (k > warp * 128 ? (k - warp * 128 + GV_WARPS * 128 - 1) / (GV_WARPS * 128) : 0);
+#pragma unroll
+  for (int it = 0; it < GA_STAGES - 1; ++it) rg.issue(it);      // the weights are on their way while X is staged
+
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool xlive = g < n;
+  if (XT == E5MA_BF16) {
+    uint8_t *xs = ring_raw + (size_t)GV_WARPS * GA_STAGES * 2048;
+    const int per_col = k / 8;                        // k is a multiple of 16
+    bool fits = true;
+    for (int idx = threadIdx.x; idx < n * per_col; idx += GV_WARPS * 32) {
+      const int j = idx / per_col, q = idx - j * per_col;
+      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(X + ((size_t)j * ldx + (size_t)q * 8) * 2));
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      uint32_t h[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xFFFF0000u);
+        const __half2 hh = __floats2half2_rn(lo, hi);
+        const float2 back = __half22float2(hh);
+        fits = fits && back.x == lo && back.y == hi;
+        h[e] = *reinterpret_cast<const uint32_t *>(&hh);
+      }
+      *reinterpret_cast<uint4 *>(xs + (size_t)j * x_pitch + (size_t)q * 16) = make_uint4(h[0], h[1], h[2], h[3]);
+    }
+    if (__syncthreads_and(fits)) ga_mainloop<AT, XT, GA_STAGES, 2>(rg, xs + (size_t)g * x_pitch, xlive, acc, acc2);
+    else ga_mainloop<AT, XT, GA_STAGES, 0>(rg, X + (size_t)g * ldx * 2, xlive, acc, acc2);
+  } else {
+    ga_mainloop<AT, XT, GA_STAGES, 1>(rg, X + (size_t)g * ldx, xlive, acc, acc2);
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) acc[e] = __fadd_rn(acc[e], acc2[e]);
+  cp_async_wait<0>();
+
+  red[warp][g][2 * t] = acc[0];
+  red[warp][g][2 * t + 1] = acc[1];
+  red[warp][g + 8][2 * t] = acc[2];
+  red[warp][g + 8][2 * t + 1] = acc[3];
+  __syncthreads();
+  const OutScalars r = out_begin(o);
+  float mx = 0.f;
+  if (threadIdx.x < 128) {
+    const int il = threadIdx.x & 15, j = threadIdx.x >> 4, i = row0 + il;
+    if (i < m && j < n) {
+      float s = red[0][il][j];
+#pragma unroll
+      for (int w = 1; w < GV_WARPS; ++w) s = __fadd_rn(s, red[w][il][j]);
+      mx = out_store(o, r, i, j, s);
+    }
+  }
+  if (o.amax) block_amax(o.amax, mx);
+}
+
+
 // Shared memory of the persistent kernel for a given problem, and the stage count that fits (0: does not fit).
 struct BulkPlan { int stages, x_pitch, smem; };
 static BulkPlan gemv_bulk_plan(int n, int k) {
@@ -908,6 +1087,27 @@ static cudaError_t gemv_async_x(int x_dtype, const uint8_t *A, int lda, const ui
   constexpr int GA_SMEM = GV_WARPS * GA_STAGES * 2048;
   const unsigned grid = (unsigned)((m + 15) / 16);
   const int kmap = (opt(OPT_GEMV_KMAP) >= 0 ? opt(OPT_GEMV_KMAP) : tuned_gemv(2)) > 0 ? 1 : 0;
+  // FP16 arithmetic (switch GEMV_F16, on by default): FP8 activations always; BF16 activations when their FP16 copy
+  // (n columns of k values, rows padded against bank conflicts) fits in 32 KiB beside the ring
+  const int x_pitch = k * 2 + 16;
+  const bool f16 = opt(OPT_GEMV_F16) != 0 && (x_dtype != E5MA_BF16 || (size_t)n * x_pitch <= 32768);
+  if (f16) {
+    const int smem = GA_SMEM + (x_dtype == E5MA_BF16 ? n * x_pitch : 0);
+#define E5B_GEMV16_CASE(XT)                                                                                                 \
+  {                                                                                                                         \
+    static SmemOptIn optin;                                                                                                 \
+    if (const cudaError_t e = optin.ensure(gemv_async16_kernel<AT, XT, GA_STAGES>, GA_SMEM + 32768)) return e;              \
+    gemv_async16_kernel<AT, XT, GA_STAGES><<<grid, GV_WARPS * 32, smem, s>>>(A, lda, X, ldx, m, n, k, kmap, x_pitch, o);    \
+  }
+    switch (x_dtype) {
+      case E5MA_BF16: E5B_GEMV16_CASE(E5MA_BF16) break;
+      case E5MA_E5M2: E5B_GEMV16_CASE(E5MA_E5M2) break;
+      case E5MA_E4M3: E5B_GEMV16_CASE(E5MA_E4M3) break;
+      default: return cudaErrorNotSupported;
+    }
+#undef E5B_GEMV16_CASE
+    return cudaGetLastError();
+  }
 #define E5B_GEMV_CASE(XT, slot_)                                                                                            \
   {                                                                                                                         \
     static SmemOptIn optin;                                                                                                 \

@@ -11,6 +11,8 @@ Two regimes, as the interface documents them:
 import numpy as np
 import pytest
 
+import oracle as orc
+
 from harness import (BF16, E4M3, E5M2, FP16, FP32, GemmCase, GemmData, check_exact, check_tolerance, force_simt,
                      reference_gemm_cases, reference_gemv_cases)
 
@@ -132,6 +134,7 @@ def test_runs_are_deterministic():
 
 
 GEMV_VARIANTS = {"async ring, interleaved k": {"GEMV_KERNEL": 1, "GEMV_KMAP": 0}, "async ring, contiguous k": {"GEMV_KERNEL": 1, "GEMV_KMAP": 1},
+                 "async ring, BF16 arithmetic only": {"GEMV_KERNEL": 1, "GEMV_F16": 0},
                  "register loads": {"GEMV_KERNEL": 0}, "row streams, 4 stages": {"GEMV_KERNEL": 3}, "row streams, 3 stages": {"GEMV_KERNEL": 3, "GEMV_STAGES": 3},
                  "FP32 pipe": {"GEMV_FMA_MAXN": 4}}
 
@@ -144,7 +147,7 @@ GEMV_VARIANTS = {"async ring, interleaved k": {"GEMV_KERNEL": 1, "GEMV_KMAP": 0}
                          ids=lambda c: c.label())
 def test_gemv_kernel_variants_within_tolerance(case, variant):
     """Every GEMV kernel the switches can select -- the cp.async ring with interleaved 128-byte k-steps and with each
-    warp on a contiguous eighth of K, register loads, the row-stream ring at both depths, the FP32-pipe kernel for
+    warp on a contiguous eighth of K (FP16 arithmetic where X allows it), the same without FP16 arithmetic, register loads, the row-stream ring at both depths, the FP32-pipe kernel for
     batches up to 4 -- gives results within the bound."""
     from e5m2effma_b200 import capi
     if case.bt == FP32:
@@ -162,3 +165,26 @@ def test_gemv_kernel_variants_within_tolerance(case, variant):
     check_tolerance(d, got, amax)
     assert route == (capi.ROUTE_GEMV_FMA if variant == "FP32 pipe" and case.n <= 4 else
                      capi.ROUTE_GEMV_ROWS if variant.startswith("row streams") else capi.ROUTE_GEMV)
+
+
+@pytest.mark.parametrize("n", [1, 2, 3])
+@pytest.mark.parametrize("special", ["too large for FP16", "below the FP16 grid", "FP16 subnormal, exact", "zeros and signs"])
+def test_gemv_bf16_activations_outside_fp16(n, special):
+    """The cp.async GEMV computes in FP16 when every BF16 activation converts exactly and in BF16 otherwise; either
+    way the result obeys the same bound.  (n = 3 is beyond what the FP16 copy of X is offered for at this k.)"""
+    from e5m2effma_b200 import capi
+    d = GemmData(GemmCase(1, 0, 200, n, 6160, E5M2, BF16, FP32, -1, -1, 1.0, 0.0, vec=1, seed=40 + n))
+    bf16 = lambda v: int(orc.encode(BF16, np.array([v], np.float32))[0])
+    vals = {"too large for FP16": [1.0e6, -7.0e4], "below the FP16 grid": [2.0 ** -30, -(2.0 ** -26)],
+            "FP16 subnormal, exact": [2.0 ** -20, -(2.0 ** -24), 3 * 2.0 ** -23], "zeros and signs": [0.0, -0.0, 65504.0, -65504.0]}[special]
+    for j in range(n):
+        for i, v in enumerate(vals):
+            d.B[j * d.ldb + 7 + 13 * i + j] = bf16(v)
+    capi.set_option("GEMV_KERNEL", 1)
+    try:
+        got, amax = d.run_gpu()
+        route = capi.last_route()
+    finally:
+        capi.set_option("GEMV_KERNEL", None)
+    assert route == capi.ROUTE_GEMV
+    check_tolerance(d, got, amax)
