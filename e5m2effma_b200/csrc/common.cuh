@@ -254,6 +254,7 @@ enum Opt {
   OPT_WIDEN_GROUPS,   // E5MA_WIDEN_GROUPS  1, 2: groups of warps that widen alternate k-blocks of a mixed FP8 x BF16 GEMM
   OPT_GEMV_FMA_MAXN,  // E5MA_GEMV_FMA_MAXN 0..4: largest batch of FP8 / BF16 activations that takes the FP32-pipe GEMV kernel
   OPT_GEMV_F16,       // E5MA_GEMV_F16      0: the cp.async GEMV never uses FP16 arithmetic (BF16 everywhere, as gemv_async_kernel)
+  OPT_TC_KSPLIT,      // E5MA_TC_KSPLIT     0: the one-CTA GEMM never splits K over CTA pairs; 1: whenever at most half of the SMs have a tile
   OPT_COUNT
 };
 int opt(Opt which);
@@ -266,7 +267,8 @@ int tuned_gemv(int key);
 
 // Which kernel the last e5ma_gemm call of this host thread launched (e5b_last_route()).
 enum Route { ROUTE_NONE = 0, ROUTE_GEMV = 1, ROUTE_GEMV_PERSISTENT = 2, ROUTE_TC_PAIR = 3, ROUTE_TC_PAIR_WIDE = 4,
-             ROUTE_TC_256 = 5, ROUTE_TC_128 = 6, ROUTE_SIMT = 7, ROUTE_TC_MIXED_PAIR = 8, ROUTE_GEMV_FMA = 9, ROUTE_GEMV_ROWS = 10 };
+             ROUTE_TC_256 = 5, ROUTE_TC_128 = 6, ROUTE_SIMT = 7, ROUTE_TC_MIXED_PAIR = 8, ROUTE_GEMV_FMA = 9, ROUTE_GEMV_ROWS = 10,
+             ROUTE_TC_256_KSPLIT = 11, ROUTE_TC_128_KSPLIT = 12 };
 void note_route(int r);
 // E5MA_OK and the properties of the current device when it is compute capability 10.x
 e5ma_status require_blackwell(const char *who, DeviceProps *out);

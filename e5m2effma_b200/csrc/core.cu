@@ -38,7 +38,7 @@ e5ma_status cuda_fail(cudaError_t e, const char *what) {
 static std::atomic<int> g_opt[OPT_COUNT];
 static const char *const kOptNames[OPT_COUNT] = {"FORCE_SIMT", "TC_PAIR", "TC_SPLIT", "TC_GRID", "TC_WIDE", "GEMV_KERNEL",
                                                  "GEMV_STAGES", "GEMV_U", "GEMV_MT", "MIXED_PAIR", "GEMV_KMAP", "WIDEN_GROUPS",
-                                                 "GEMV_FMA_MAXN", "GEMV_F16"};
+                                                 "GEMV_FMA_MAXN", "GEMV_F16", "TC_KSPLIT"};
 static void opt_init() {
   static std::once_flag once;
   std::call_once(once, [] {

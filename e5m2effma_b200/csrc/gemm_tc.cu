@@ -34,7 +34,12 @@
 //     that were slower on this part: widening into tensor memory with the MMA reading its A operand
 //     from there (each such MMA took ~280 clocks whatever its N), separate rings for raw and widened
 //     data, CTA pairs (the extra cross-CTA signalling lengthens the per-stage chain).
-//   * No cluster features are used: every CTA loads its own operand boxes.
+//   * Few tiles, long K (a column shard of a weight-gradient GEMM: 64 tiles of K = 65536 on 148 SMs): the kernel
+//     is launched as clusters of two CTAs that share one tile, each adding up one half of the k-blocks into its
+//     own tensor memory.  When both are done, the second CTA writes its FP32 partial sums into the first one's
+//     (now idle) stage ring through distributed shared memory, thread for thread, and the first adds them to its
+//     own in a fixed order (deterministic) and runs the epilogue.  No scratch memory, no atomics.
+//   * Otherwise no cluster features are used: every CTA loads its own operand boxes.
 //
 // Every wait on an mbarrier is bounded.  A wait that runs out records a fault word, raises a
 // block-wide abort flag that every role polls, and the CTA leaves through the common exit, where
@@ -76,8 +81,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
   // stage ring at the first 1 KiB boundary (the swizzle pattern repeats every 1024 bytes)
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *after_ring = smem_raw + (ring - smem_u32(smem_raw)) + C::STAGES * C::STAGE_BYTES;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(after_ring);   // full[S], empty[S], acc_full[2], acc_empty[2], ready[S]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * C::STAGES + 4);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(after_ring);   // full[S], empty[S], acc_full[2], acc_empty[2], ready[S], xfer_go, xfer_done
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * C::STAGES + 6);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   const auto full_bar = [&](int s) { return bar0 + 8u * s; };
@@ -85,15 +90,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
   const auto acc_full = [&](int b) { return bar0 + 8u * (2 * C::STAGES + b); };
   const auto acc_empty = [&](int b) { return bar0 + 8u * (2 * C::STAGES + 2 + b); };
   const auto ready_bar = [&](int s) { return bar0 + 8u * (2 * C::STAGES + 4 + s); };   // converted operand in place
+  const uint32_t xfer_go = bar0 + 8u * (3 * C::STAGES + 4), xfer_done = xfer_go + 8u;  // K split over a CTA pair
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_i = (m + BI - 1) / BI, tiles_j = (n + BM - 1) / BM, tiles = tiles_i * tiles_j;
-  const int kblocks = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
+  const int kblocks_all = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
+  // K split: the two CTAs of a cluster take the same (single) tile and one half of its k-blocks each
+  const bool ksplit = md.ksplit != 0;
+  const uint32_t crank = ksplit ? cluster_rank() : 0u;
+  const int kb_first = crank ? kblocks_all / 2 : 0;
+  const int kblocks = ksplit ? (crank ? kblocks_all - kblocks_all / 2 : kblocks_all / 2) : kblocks_all;
+  const int item_first = ksplit ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int item_step = ksplit ? (1 << 30) : (int)gridDim.x;
 
   // Work items.  Normally one item = one tile, dealt round-robin to the CTAs.  When the last round would
   // keep at most half of the CTAs busy, its tiles are cut into two half tiles (BI / 2 rows: map_ih boxes,
   // idesc_half) so that the round takes half as long.  Every role derives the same list from this.
-  const int grid_n = gridDim.x;
+  const int grid_n = ksplit ? tiles : (int)gridDim.x;
   const int full_items = (tiles / grid_n) * grid_n, rem = tiles - full_items;
   const bool split = md.split && rem > 0 && 2 * rem <= grid_n;
   const int items = split ? full_items + 2 * rem : tiles;
@@ -111,6 +124,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); mbar_init(ready_bar(s), EPI_WARPS / md.wgroups); }
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), EPI_WARPS); }
+    mbar_init(xfer_go, 1);
+    mbar_init(xfer_done, 32 * EPI_WARPS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -122,6 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (ksplit) cluster_sync_all();      // both CTAs' barriers exist before either signals the other
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
@@ -129,7 +145,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < items && ok; t += gridDim.x) {
+      for (int t = item_first; t < items && ok; t += item_step) {
         int i0, j0, rows;
         item_at(t, i0, j0, rows);
         const bool half_tile = rows != BI;
@@ -137,7 +153,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
         // were read last and are still in L2 (the sum does not care about the order of its k-blocks)
         const bool backwards = ((t / (int)gridDim.x) & 1) != 0;
         for (int kq = 0; kq < kblocks; ++kq, ++it) {
-          const int kb = backwards ? kblocks - 1 - kq : kq;
+          const int kb = kb_first + (backwards ? kblocks - 1 - kq : kq);
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, (1u << 24) | (uint32_t)kb)) { ok = false; break; }
@@ -170,7 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0, lt = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < items && ok; t += gridDim.x, ++lt) {
+      for (int t = item_first; t < items && ok; t += item_step, ++lt) {
         int i0, j0, rows;
         item_at(t, i0, j0, rows);
         const uint32_t idesc_t = rows != BI ? idesc_half : idesc;
@@ -210,7 +226,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     float mx = 0.f;
     uint32_t lt = 0, it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < items && ok; t += gridDim.x, ++lt) {
+    for (int t = item_first; t < items && ok; t += item_step, ++lt) {
       int i0, j0, rows;
       item_at(t, i0, j0, rows);
       if (CONV != 0) {
@@ -254,10 +270,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
         if (o.bias) bias_i = load_elem(o.bias_dtype, o.bias, (size_t)j, 1.f);
       }
       const uint32_t t_lane = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BI;
-      for (int c0 = half * (BI / 2); c0 < (half + 1) * (BI / 2); c0 += 32) {
+      // K split: the partial sums of the second CTA travel through the first CTA's stage ring, which is idle once that
+      // CTA's accumulator is complete: slot (chunk * 8 + v) * 256 + thread, 16 bytes each, written and read by the same
+      // thread index of the two CTAs
+      const uint32_t xslot = ring + (uint32_t)(threadIdx.x - 64) * 16u;
+      if (ksplit && crank == 0) {
+        if (threadIdx.x == 64) mbar_arrive_cluster(map_to_rank(xfer_go, 1));     // my ring is free
+        ok = mbar_wait_cluster(xfer_done, 0, abort_flag, (6u << 24) | (uint32_t)warp);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+      }
+      if (ksplit && crank == 1) {
+        ok = mbar_wait_cluster(xfer_go, 0, abort_flag, (7u << 24) | (uint32_t)warp);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        const uint32_t remote = map_to_rank(xslot, 0);
+        int chunk = 0;
+        for (int c0 = half * (BI / 2); c0 < (half + 1) * (BI / 2); c0 += 32, ++chunk) {
+          if (c0 >= rows || i0 + c0 >= m) break;   // warp-uniform
+          float acc[32];
+          tmem_ld32(t_lane + c0, acc);
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote + (uint32_t)(chunk * 8 + v) * 4096u),
+                         "f"(acc[4 * v]), "f"(acc[4 * v + 1]), "f"(acc[4 * v + 2]), "f"(acc[4 * v + 3]) : "memory");
+        }
+        mbar_arrive_cluster(map_to_rank(xfer_done, 0));     // every thread releases its own stores
+        tc_fence_before();
+        continue;                                           // the first CTA runs the epilogue
+      }
+      int chunk = 0;
+      for (int c0 = half * (BI / 2); c0 < (half + 1) * (BI / 2); c0 += 32, ++chunk) {
         if (c0 >= rows || i0 + c0 >= m) break;   // warp-uniform
         float acc[32];
         tmem_ld32(t_lane + c0, acc);
+        if (ksplit) {
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            float4 p;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(p.x), "=f"(p.y), "=f"(p.z), "=f"(p.w)
+                         : "r"(xslot + (uint32_t)(chunk * 8 + v) * 4096u) : "memory");
+            acc[4 * v] = __fadd_rn(acc[4 * v], p.x);
+            acc[4 * v + 1] = __fadd_rn(acc[4 * v + 1], p.y);
+            acc[4 * v + 2] = __fadd_rn(acc[4 * v + 2], p.z);
+            acc[4 * v + 3] = __fadd_rn(acc[4 * v + 3], p.w);
+          }
+        }
         if (col_ok) {
           if (md.transposed) mx = fmaxf(mx, drain32_t<DT>(o, r, acc, j, i0 + c0, m, as_i, sb_const, bias_i));
           else mx = fmaxf(mx, drain32<DT>(o, r, md, acc, i0 + c0, j, m, as_const, sbj));
@@ -278,9 +336,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     }
   }
 
-  // common exit: everybody meets, then the allocating warp releases tensor memory
+  // common exit: everybody meets (with a K split: both CTAs of the pair, so that neither leaves while the other may
+  // still signal it or write into its shared memory), then the allocating warp releases tensor memory
   tc_fence_before();
   __syncthreads();
+  if (ksplit) cluster_sync_all();
   if (*abort_flag && threadIdx.x == 0) {
     // give copies that may still be in flight time to land before the shared memory is reused
     const unsigned long long t0 = clock64();
@@ -292,6 +352,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
+}
+
+// Two CTAs per tile, half of K each, when that keeps more SMs busy: at most half of the SMs would have a tile, and
+// the mainloop (at least 64 k-blocks) is long next to the exchange of the partial sums (~2 us).
+static bool ksplit_wanted(int tiles, int kblocks, int sms) {
+  const int sw = opt(OPT_TC_KSPLIT);
+  if (sw == 0 || 2 * tiles > sms || kblocks < 2) return false;
+  return sw == 1 || kblocks >= 64;
 }
 
 template <int BI, int KIND, int DT, int CONV, int FT>
@@ -306,6 +374,25 @@ static cudaError_t launch_cfg(const CUtensorMap &mi, const CUtensorMap &mj, cons
   const int cap = opt(OPT_TC_GRID);   // experiments: fewer CTAs than SMs
   if (cap > 0 && cap < grid) grid = cap;
   note_route(BI == 256 ? ROUTE_TC_256 : ROUTE_TC_128);
+  if (ksplit_wanted(tiles, (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES, sms)) {
+    // K split over CTA pairs: one cluster of two CTAs per tile (switch TC_KSPLIT: 0 never, 1 whenever the tiles allow it)
+    EpiMode mk = md;
+    mk.ksplit = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * tiles);
+    cfg.blockDim = dim3(C::NTHREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    note_route(BI == 256 ? ROUTE_TC_256_KSPLIT : ROUTE_TC_128_KSPLIT);
+    return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BI, KIND, DT, CONV, FT>, mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, mk);
+  }
   gemm_tc_kernel<BI, KIND, DT, CONV, FT><<<grid, C::NTHREADS, C::SMEM_BYTES, s>>>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md);
   return cudaGetLastError();
 }
@@ -510,7 +597,8 @@ cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const
   const int kconv = conv ? 2 : 0;                              // after the swap the FP8 operand is always on the M side
   const int tiles256 = ((en + 255) / 256) * ((em + BM - 1) / BM);
   const int tiles128 = ((en + 127) / 128) * ((em + BM - 1) / BM);
-  const bool underfilled = tiles256 < sms && tiles128 > tiles256 && tiles256 * 4 < sms * 3;   // 256-row tiles would idle a quarter of the SMs
+  // 256-row tiles would idle a quarter of the SMs -- unless two CTAs can share each of them (K split), which beats smaller tiles
+  const bool underfilled = tiles256 < sms && tiles128 > tiles256 && tiles256 * 4 < sms * 3 && !(en > 128 && ksplit_wanted(tiles256, kblocks, sms));
   const bool wide = en > 128 && !underfilled && (tiles256 >= sms || en % 256 == 0 || en > 1024);
   const int bi = wide ? 256 : 128;
   CUtensorMap mi, mj, mih;   // mih: the N-side operand with half-height boxes, for the half tiles of the last round

@@ -57,6 +57,29 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same wait with cluster-scope acquire: for barriers on which another CTA of the cluster arrives (release at
+// cluster scope) after writing into this CTA's shared memory.
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned int who) {
+  if (mbar_try_cluster(bar, parity)) return true;
+  const unsigned long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_cluster(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if ((unsigned long long)(clock64() - t0) > WAIT_LIMIT) {
+      *abort_flag = 1;
+      atomicCAS(&g_fault, 0u, who);
+      return false;
+    }
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
@@ -214,9 +237,10 @@ __device__ __forceinline__ void store32(void *p, const float v[32], float qs) {
 // access (base and leading dimension multiples of 16 bytes) and whether bias / C have a dtype the
 // vector path reads directly.
 // wgroups: into how many groups the epilogue warps split to widen alternate k-blocks of a mixed problem (1, 2).
+// ksplit: the one-CTA kernel runs as 2-CTA clusters, each CTA adding up one half of K of the same tile.
 // split: the last partial wave of tiles is cut into half tiles.  transposed: the kernel was given the
 // operands in swapped roles (TMEM lanes are rows i, TMEM columns are columns j) and its m / n are swapped.
-struct EpiMode { int vec; int split; int transposed; int mn_n; int mn_m; int wgroups; };   // mn_n / mn_m: the N-side / M-side operand is stored MN-contiguous
+struct EpiMode { int vec; int split; int transposed; int mn_n; int mn_m; int wgroups; int ksplit; };   // mn_n / mn_m: the N-side / M-side operand is stored MN-contiguous
 
 // One thread's 32 accumulators: column j, rows ib .. ib+31.  Fast path when the 32 rows are all
 // inside the matrix and vector access is allowed; otherwise element by element.
