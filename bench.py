@@ -622,7 +622,8 @@ def measure_sharded(name, w, rot, tm, world, rank, dev, steps, warmup, sampler, 
 # ---------------------------------------------------------------------------------------------------------------
 ROUTE_NAMES = ["none", "gemv cp.async ring", "gemv bulk-copy ring", "tcgen05 CTA pairs 256x256", "tcgen05 CTA pairs, wide tiles",
                "tcgen05 one CTA, 256-row tiles", "tcgen05 one CTA, 128-row tiles", "CUDA cores (FP32 FMA chain)", "tcgen05 CTA pairs, mixed", "gemv row streams, FP32 FMA pipe", "gemv row streams, mma.sync",
-               "tcgen05 one CTA, 256-row tiles, K split over CTA pairs", "tcgen05 one CTA, 128-row tiles, K split over CTA pairs"]
+               "tcgen05 one CTA, 256-row tiles, K split over CTA pairs", "tcgen05 one CTA, 128-row tiles, K split over CTA pairs",
+               "tcgen05 one CTA, 256-row tiles, last round K-split", "tcgen05 one CTA, 128-row tiles, last round K-split"]
 
 
 def gemm_rows(tm, dev, local, shrink, pk, use_graph):

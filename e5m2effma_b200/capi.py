@@ -80,7 +80,8 @@ def gemm_fault():
 
 
 ROUTE_NONE, ROUTE_GEMV, ROUTE_GEMV_PERSISTENT, ROUTE_TC_PAIR, ROUTE_TC_PAIR_WIDE, ROUTE_TC_256, ROUTE_TC_128, ROUTE_SIMT, \
-    ROUTE_TC_MIXED_PAIR, ROUTE_GEMV_FMA, ROUTE_GEMV_ROWS, ROUTE_TC_256_KSPLIT, ROUTE_TC_128_KSPLIT = range(13)
+    ROUTE_TC_MIXED_PAIR, ROUTE_GEMV_FMA, ROUTE_GEMV_ROWS, ROUTE_TC_256_KSPLIT, ROUTE_TC_128_KSPLIT, \
+    ROUTE_TC_256_KTAIL, ROUTE_TC_128_KTAIL = range(15)
 
 
 def set_option(name, value):

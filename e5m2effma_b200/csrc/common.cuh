@@ -268,7 +268,7 @@ int tuned_gemv(int key);
 // Which kernel the last e5ma_gemm call of this host thread launched (e5b_last_route()).
 enum Route { ROUTE_NONE = 0, ROUTE_GEMV = 1, ROUTE_GEMV_PERSISTENT = 2, ROUTE_TC_PAIR = 3, ROUTE_TC_PAIR_WIDE = 4,
              ROUTE_TC_256 = 5, ROUTE_TC_128 = 6, ROUTE_SIMT = 7, ROUTE_TC_MIXED_PAIR = 8, ROUTE_GEMV_FMA = 9, ROUTE_GEMV_ROWS = 10,
-             ROUTE_TC_256_KSPLIT = 11, ROUTE_TC_128_KSPLIT = 12 };
+             ROUTE_TC_256_KSPLIT = 11, ROUTE_TC_128_KSPLIT = 12, ROUTE_TC_256_KTAIL = 13, ROUTE_TC_128_KTAIL = 14 };
 void note_route(int r);
 // E5MA_OK and the properties of the current device when it is compute capability 10.x
 e5ma_status require_blackwell(const char *who, DeviceProps *out);

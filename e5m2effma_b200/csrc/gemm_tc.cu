@@ -38,7 +38,10 @@
 //     is launched as clusters of two CTAs that share one tile, each adding up one half of the k-blocks into its
 //     own tensor memory.  When both are done, the second CTA writes its FP32 partial sums into the first one's
 //     (now idle) stage ring through distributed shared memory, thread for thread, and the first adds them to its
-//     own in a fixed order (deterministic) and runs the epilogue.  No scratch memory, no atomics.
+//     own in a fixed order (deterministic) and runs the epilogue.  No scratch memory, no atomics.  The same is
+//     done for the tiles of a last round that would keep at most half of the SMs busy (512 tiles on 148 SMs: 68 in
+//     the fourth round): the persistent CTAs are launched as clusters of two, and after their own tiles the two CTAs
+//     of a cluster share one of the remaining tiles.
 //   * Otherwise no cluster features are used: every CTA loads its own operand boxes.
 //
 // Every wait on an mbarrier is bounded.  A wait that runs out records a fault word, raises a
@@ -95,21 +98,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_i = (m + BI - 1) / BI, tiles_j = (n + BM - 1) / BM, tiles = tiles_i * tiles_j;
   const int kblocks_all = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
-  // K split: the two CTAs of a cluster take the same (single) tile and one half of its k-blocks each
-  const bool ksplit = md.ksplit != 0;
-  const uint32_t crank = ksplit ? cluster_rank() : 0u;
-  const int kb_first = crank ? kblocks_all / 2 : 0;
-  const int kblocks = ksplit ? (crank ? kblocks_all - kblocks_all / 2 : kblocks_all / 2) : kblocks_all;
-  const int item_first = ksplit ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
-  const int item_step = ksplit ? (1 << 30) : (int)gridDim.x;
+  // K split (md.ksplit: 1 every tile, 2 the tiles of the last, partly filled round): the two CTAs of a cluster take
+  // the same tile and one half of its k-blocks each; such a tile is the last item of both CTAs
+  const int ksmode = md.ksplit;
+  const uint32_t crank = ksmode ? cluster_rank() : 0u;
 
   // Work items.  Normally one item = one tile, dealt round-robin to the CTAs.  When the last round would
   // keep at most half of the CTAs busy, its tiles are cut into two half tiles (BI / 2 rows: map_ih boxes,
   // idesc_half) so that the round takes half as long.  Every role derives the same list from this.
-  const int grid_n = ksplit ? tiles : (int)gridDim.x;
-  const int full_items = (tiles / grid_n) * grid_n, rem = tiles - full_items;
-  const bool split = md.split && rem > 0 && 2 * rem <= grid_n;
-  const int items = split ? full_items + 2 * rem : tiles;
+  const int grid_n = gridDim.x;
+  const int full_items = ksmode == 1 ? 0 : (tiles / grid_n) * grid_n, rem = tiles - full_items;
+  const bool split = md.split && ksmode == 0 && rem > 0 && 2 * rem <= grid_n;
+  const int items = ksmode ? full_items : (split ? full_items + 2 * rem : tiles);   // dealt round-robin to single CTAs
+  // this CTA's sequence: its share of `items`, then (K split) the tile full_items + cluster index shared with the peer
+  const int my_main = (int)blockIdx.x < items ? (items - 1 - (int)blockIdx.x) / grid_n + 1 : 0;
+  const int my_items = my_main + (ksmode && (int)(blockIdx.x >> 1) < rem ? 1 : 0);
+  const auto seq_at = [&](int q, int &t, bool &shared, int &kb_first, int &kblocks) {
+    shared = q >= my_main;
+    t = shared ? full_items + (int)(blockIdx.x >> 1) : (int)blockIdx.x + q * grid_n;
+    kb_first = shared && crank ? kblocks_all / 2 : 0;
+    kblocks = shared ? (crank ? kblocks_all - kblocks_all / 2 : kblocks_all / 2) : kblocks_all;
+  };
   const auto item_at = [&](int item, int &i0, int &j0, int &rows) {
     int tile = item, hf = 0;
     rows = BI;
@@ -137,7 +146,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (ksplit) cluster_sync_all();      // both CTAs' barriers exist before either signals the other
+  if (ksmode) cluster_sync_all();      // both CTAs' barriers exist before either signals the other
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
@@ -145,13 +154,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = item_first; t < items && ok; t += item_step) {
-        int i0, j0, rows;
+      for (int q = 0; q < my_items && ok; ++q) {
+        int t, kb_first, kblocks, i0, j0, rows;
+        bool shared;
+        seq_at(q, t, shared, kb_first, kblocks);
         item_at(t, i0, j0, rows);
         const bool half_tile = rows != BI;
         // successive tiles of a CTA walk K in opposite directions: the next tile starts with the k-blocks that
         // were read last and are still in L2 (the sum does not care about the order of its k-blocks)
-        const bool backwards = ((t / (int)gridDim.x) & 1) != 0;
+        const bool backwards = !shared && (q & 1) != 0;
         for (int kq = 0; kq < kblocks; ++kq, ++it) {
           const int kb = kb_first + (backwards ? kblocks - 1 - kq : kq);
           const int s = it % C::STAGES;
@@ -186,8 +197,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0, lt = 0;
       bool ok = true;
-      for (int t = item_first; t < items && ok; t += item_step, ++lt) {
-        int i0, j0, rows;
+      for (int q = 0; q < my_items && ok; ++q, ++lt) {
+        int t, kb_first, kblocks, i0, j0, rows;
+        bool shared;
+        seq_at(q, t, shared, kb_first, kblocks);
         item_at(t, i0, j0, rows);
         const uint32_t idesc_t = rows != BI ? idesc_half : idesc;
         const uint32_t buf = lt & 1u, use = lt >> 1;
@@ -226,8 +239,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
     float mx = 0.f;
     uint32_t lt = 0, it = 0;
     bool ok = true;
-    for (int t = item_first; t < items && ok; t += item_step, ++lt) {
-      int i0, j0, rows;
+    for (int q = 0; q < my_items && ok; ++q, ++lt) {
+      int t, kb_first, kblocks, i0, j0, rows;
+      bool shared;
+      seq_at(q, t, shared, kb_first, kblocks);
       item_at(t, i0, j0, rows);
       if (CONV != 0) {
         // Mixed pairs: these warps first widen the FP8 operand of every k-block of the tile (widen_block), then
@@ -274,13 +289,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
       // CTA's accumulator is complete: slot (chunk * 8 + v) * 256 + thread, 16 bytes each, written and read by the same
       // thread index of the two CTAs
       const uint32_t xslot = ring + (uint32_t)(threadIdx.x - 64) * 16u;
-      if (ksplit && crank == 0) {
+      if (shared && crank == 0) {
         if (threadIdx.x == 64) mbar_arrive_cluster(map_to_rank(xfer_go, 1));     // my ring is free
         ok = mbar_wait_cluster(xfer_done, 0, abort_flag, (6u << 24) | (uint32_t)warp);
         ok = __all_sync(0xFFFFFFFFu, ok);
         if (!ok) break;
       }
-      if (ksplit && crank == 1) {
+      if (shared && crank == 1) {
         ok = mbar_wait_cluster(xfer_go, 0, abort_flag, (7u << 24) | (uint32_t)warp);
         ok = __all_sync(0xFFFFFFFFu, ok);
         if (!ok) break;
@@ -304,7 +319,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
         if (c0 >= rows || i0 + c0 >= m) break;   // warp-uniform
         float acc[32];
         tmem_ld32(t_lane + c0, acc);
-        if (ksplit) {
+        if (shared) {
 #pragma unroll
           for (int v = 0; v < 8; ++v) {
             float4 p;
@@ -340,7 +355,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_i, const __grid_constant_
   // still signal it or write into its shared memory), then the allocating warp releases tensor memory
   tc_fence_before();
   __syncthreads();
-  if (ksplit) cluster_sync_all();
+  if (ksmode) cluster_sync_all();
   if (*abort_flag && threadIdx.x == 0) {
     // give copies that may still be in flight time to land before the shared memory is reused
     const unsigned long long t0 = clock64();
@@ -362,6 +377,15 @@ static bool ksplit_wanted(int tiles, int kblocks, int sms) {
   return sw == 1 || kblocks >= 64;
 }
 
+// More tiles than SMs, and the last round would keep at most half of them busy: its tiles are shared by CTA pairs
+// (half of K each) instead of being cut into half tiles, which a mixed pair does not run any faster.
+static bool ksplit_tail_wanted(int tiles, int kblocks, int sms) {
+  const int sw = opt(OPT_TC_KSPLIT), g = sms & ~1;
+  if (sw == 0 || g < 2 || tiles <= g || kblocks < 2) return false;
+  const int rem = tiles % g;
+  return rem > 0 && 2 * rem <= g && (sw == 1 || kblocks >= 64);
+}
+
 template <int BI, int KIND, int DT, int CONV, int FT>
 static cudaError_t launch_cfg(const CUtensorMap &mi, const CUtensorMap &mj, const CUtensorMap &mih, int m, int n,
                               int k_bytes, uint32_t idesc, uint32_t idesc_half, const OutDesc &o, const EpiMode &md, int sms,
@@ -374,12 +398,15 @@ static cudaError_t launch_cfg(const CUtensorMap &mi, const CUtensorMap &mj, cons
   const int cap = opt(OPT_TC_GRID);   // experiments: fewer CTAs than SMs
   if (cap > 0 && cap < grid) grid = cap;
   note_route(BI == 256 ? ROUTE_TC_256 : ROUTE_TC_128);
-  if (ksplit_wanted(tiles, (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES, sms)) {
-    // K split over CTA pairs: one cluster of two CTAs per tile (switch TC_KSPLIT: 0 never, 1 whenever the tiles allow it)
+  const int kb_all = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
+  const int ks = ksplit_wanted(tiles, kb_all, sms) ? 1 : (cap <= 0 && ksplit_tail_wanted(tiles, kb_all, sms) ? 2 : 0);
+  if (ks) {
+    // K split over CTA pairs (switch TC_KSPLIT: 0 never, 1 whenever the tiles allow it).  1: one cluster of two CTAs
+    // per tile.  2: persistent CTAs as usual, launched as clusters of two, which share the tiles of the last round.
     EpiMode mk = md;
-    mk.ksplit = 1;
+    mk.ksplit = ks;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * tiles);
+    cfg.gridDim = dim3(ks == 1 ? 2 * tiles : (sms & ~1));
     cfg.blockDim = dim3(C::NTHREADS);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = s;
@@ -390,7 +417,7 @@ static cudaError_t launch_cfg(const CUtensorMap &mi, const CUtensorMap &mj, cons
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    note_route(BI == 256 ? ROUTE_TC_256_KSPLIT : ROUTE_TC_128_KSPLIT);
+    note_route(ks == 1 ? (BI == 256 ? ROUTE_TC_256_KSPLIT : ROUTE_TC_128_KSPLIT) : (BI == 256 ? ROUTE_TC_256_KTAIL : ROUTE_TC_128_KTAIL));
     return cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BI, KIND, DT, CONV, FT>, mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, mk);
   }
   gemm_tc_kernel<BI, KIND, DT, CONV, FT><<<grid, C::NTHREADS, C::SMEM_BYTES, s>>>(mi, mj, mih, m, n, k_bytes, idesc, idesc_half, o, md);

@@ -40,7 +40,8 @@ int e5b_tuned_plan(int elem_bytes, int m, int n, int k);
  * 256 x 128 / 128 x 128 tiles, 7 ascending-k CUDA-core GEMM, 8 CTA-pair GEMM for FP8 x BF16 pairs,
  * 9 streaming GEMV on the FP32 FMA pipe (FP32 activations, and small batches of the other formats),
  * 10 streaming GEMV with row streams (the tensor-core arithmetic of 1 behind block-wide copies of whole row segments),
- * 11 / 12 the kernels of 5 / 6 with K split over pairs of CTAs (few tiles, long K).
+ * 11 / 12 the kernels of 5 / 6 with K split over pairs of CTAs (few tiles, long K), 13 / 14 the same kernels with only
+ * the tiles of the last, partly filled round shared by CTA pairs.
  * The tests use it to assert that a case really ran on the kernel it was written for.
  * No counterpart in the reference (one GEMM kernel, one GEMV kernel). */
 int e5b_last_route(void);

@@ -105,7 +105,7 @@ def test_reference_benchmark_rows_sampled_columns(name):
     w = workloads.make(name, torch.device("cuda", 0))
     _run(w)
     expected = {"row_tn": (capi.ROUTE_TC_PAIR, capi.ROUTE_TC_PAIR_WIDE), "row_tn_e4m3": (capi.ROUTE_TC_PAIR, capi.ROUTE_TC_PAIR_WIDE),
-                "row_tn_f32": (capi.ROUTE_SIMT,)}.get(name, (capi.ROUTE_TC_256, capi.ROUTE_TC_128))
+                "row_tn_f32": (capi.ROUTE_SIMT,)}.get(name, (capi.ROUTE_TC_256, capi.ROUTE_TC_128, capi.ROUTE_TC_256_KTAIL, capi.ROUTE_TC_128_KTAIL))
     assert capi.last_route() in expected
     _check_columns(w, [(0, 4), (2047, 2051), (4092, 4096)])
 

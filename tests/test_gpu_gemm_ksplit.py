@@ -55,3 +55,26 @@ def test_k_split_is_taken_by_a_wgrad_shard_and_can_be_switched_off():
     finally:
         capi.set_option("TC_KSPLIT", None)
     check_tolerance(d, got0, amax0)
+
+
+@pytest.mark.parametrize("case", [GemmCase(1, 0, 2048, 1280, 512, E5M2, BF16, FP32, -1, -1, 1.0, 1.0, seed=441, tight=True),
+                                  GemmCase(1, 0, 2000, 1300, 272, E5M2, E4M3, BF16, -1, BF16, 1.25, 0.0, vec=3, seed=442),
+                                  GemmCase(0, 0, 1300, 2100, 144, BF16, BF16, FP32, BF16, -1, 1.0, 0.5, seed=443),
+                                  GemmCase(0, 1, 2560, 1100, 1040, BF16, E5M2, E5M2, -1, -1, 1.0, 0.0, vec=2, seed=444)], ids=lambda c: c.label())
+def test_forced_k_split_of_the_last_round(case):
+    """More tiles than SMs with a sparse last round: the persistent CTAs run as clusters of two and share those tiles."""
+    from e5m2effma_b200 import capi
+    capi.set_option("TC_KSPLIT", 1)
+    capi.set_option("TC_PAIR", 0)
+    try:
+        d = GemmData(case)
+        got, amax = d.run_gpu()
+        route = capi.last_route()
+        again, _ = d.run_gpu()
+    finally:
+        capi.set_option("TC_KSPLIT", None)
+        capi.set_option("TC_PAIR", None)
+    assert route in (capi.ROUTE_TC_256_KTAIL, capi.ROUTE_TC_128_KTAIL), route
+    assert capi.gemm_fault() == 0
+    check_tolerance(d, got, amax)
+    assert np.array_equal(got.view(np.uint8), again.view(np.uint8)), "two runs of the same problem differ"

@@ -62,7 +62,8 @@ def test_same_problems_on_the_one_cta_kernel(case):
     finally:
         capi.set_option("MIXED_PAIR", None)
     check_tolerance(d, got, amax)
-    assert route in (capi.ROUTE_TC_256, capi.ROUTE_TC_128) and capi.gemm_fault() == 0
+    one_cta = (capi.ROUTE_TC_256, capi.ROUTE_TC_128, capi.ROUTE_TC_256_KSPLIT, capi.ROUTE_TC_128_KSPLIT, capi.ROUTE_TC_256_KTAIL, capi.ROUTE_TC_128_KTAIL)
+    assert route in one_cta and capi.gemm_fault() == 0
 
 
 def test_mixed_pair_kernel_is_deterministic():
