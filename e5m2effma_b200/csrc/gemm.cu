@@ -12,48 +12,91 @@
 
 namespace e5b {
 
-// ---- CUDA-core GEMM: 64 x 64 output tile, 16-deep k slices, 4 x 4 outputs per thread ------------
-constexpr int ST = 64, SK = 16;
+// ---- CUDA-core GEMM: 128 x 128 output tile, 16-deep k slices, 8 x 8 outputs per thread -----------
+// The classic register-tiled FP32 GEMM (what the reference's gemm_kernel is, src/gemm_e5m2effma.cuh:117-233): 256
+// threads, every thread owns two groups of four rows and two groups of four columns of the tile (so that its
+// shared-memory reads are 16-byte vectors without bank conflicts) and performs 64 FMAs per four such reads.  The
+// next k slice is fetched into registers (eight elements of each operand per thread, one vector load along the
+// operand's contiguous direction, decoded to FP32) while the current one is being multiplied.  Every output is one
+// FMA chain in ascending k starting from zero: bit-identical to the host emulation, whatever the tile shape.
+constexpr int ST = 128, SK = 16, SP = ST + 4;
 
-// element (r, kk) of an operand whose r index is the outer one: K-contiguous storage puts it at
-// r * ld + kk, otherwise at kk * ld + r
-__device__ __forceinline__ float operand_at(int t, const uint8_t *p, bool kc, int ld, int r, int kk) {
-  const size_t idx = kc ? (size_t)r * ld + kk : (size_t)kk * ld + r;
-  return load_elem(t, p, idx, 1.f);
+// eight consecutive elements of an operand of dtype t starting at element idx (a multiple of 8) -> FP32, exact
+__device__ __forceinline__ void load8_f32(int t, const uint8_t *p, size_t idx, float v[8]) {
+  if (t == E5MA_FP32) {
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(p + idx * 4)), b = __ldg(reinterpret_cast<const float4 *>(p + idx * 4) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else if (t == E5MA_BF16) {
+    const uint4 q = __ldg(reinterpret_cast<const uint4 *>(p + idx * 2));
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { v[2 * e] = __uint_as_float(w[e] << 16); v[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u); }
+  } else {
+    const uint2 q = __ldg(reinterpret_cast<const uint2 *>(p + idx));
+    if (t == E5MA_E5M2) { fp8x4_to_f32<E5MA_E5M2>(q.x, v); fp8x4_to_f32<E5MA_E5M2>(q.y, v + 4); }
+    else { fp8x4_to_f32<E5MA_E4M3>(q.x, v); fp8x4_to_f32<E5MA_E4M3>(q.y, v + 4); }
+  }
 }
 
-__global__ void __launch_bounds__(256) gemm_simt_kernel(int ta, int tb, bool a_kc, bool b_kc,
-                                                        const uint8_t *__restrict__ A, int lda,
-                                                        const uint8_t *__restrict__ B, int ldb, int m, int n, int k,
-                                                        OutDesc o) {
-  __shared__ __align__(16) float As[SK][ST + 4], Bs[SK][ST + 4];
+// This thread's eight elements of the k slice starting at k0 of an operand whose tile starts at row r0 (rows: m / n
+// index, `rows` of them in all).  K-contiguous storage: row r0 + (t & 127), k0 + 8 (t >> 7) .. + 8.  Otherwise: k row
+// k0 + (t >> 4), rows r0 + 8 (t & 15) .. + 8.  Rows beyond the operand read as zero.
+__device__ __forceinline__ void fetch8(int dt, const uint8_t *p, bool kc, int ld, int r0, int rows, int k0, int t, float v[8]) {
+  if (kc) {
+    const int r = r0 + (t & 127);
+    if (r < rows) load8_f32(dt, p, (size_t)r * ld + k0 + 8 * (t >> 7), v);
+    else
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+  } else {
+    const int r = r0 + 8 * (t & 15);
+    const size_t base = (size_t)(k0 + (t >> 4)) * ld + r;
+    if (r + 8 <= rows) load8_f32(dt, p, base, v);
+    else
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = r + e < rows ? load_elem(dt, p, base + e, 1.f) : 0.f;
+  }
+}
+__device__ __forceinline__ void stash8(float (*S)[SP], bool kc, int t, const float v[8]) {
+  if (kc) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) S[8 * (t >> 7) + e][t & 127] = v[e];
+  } else {
+    float *dst = &S[t >> 4][8 * (t & 15)];
+    *reinterpret_cast<float4 *>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4 *>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+__global__ void __launch_bounds__(256, 2) gemm_simt_kernel(int ta, int tb, bool a_kc, bool b_kc,
+                                                           const uint8_t *__restrict__ A, int lda,
+                                                           const uint8_t *__restrict__ B, int ldb, int m, int n, int k,
+                                                           OutDesc o) {
+  __shared__ __align__(16) float As[SK][SP], Bs[SK][SP];
   const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
   const int i0 = blockIdx.y * ST, j0 = blockIdx.x * ST;
-  float acc[4][4];
+  float acc[8][8];
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int x = 0; x < 8; ++x)
 #pragma unroll
-    for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+    for (int y = 0; y < 8; ++y) acc[x][y] = 0.f;
 
+  float pa[8], pb[8];
+  if (k > 0) { fetch8(ta, A, a_kc, lda, i0, m, 0, t, pa); fetch8(tb, B, b_kc, ldb, j0, n, 0, t, pb); }
   for (int k0 = 0; k0 < k; k0 += SK) {
-    // 1024 elements per operand tile, 4 per thread, walking along the contiguous storage direction
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int ra = a_kc ? t >> 2 : (t & 15) * 4 + e, ka = a_kc ? (t & 3) * 4 + e : t >> 4;
-      As[ka][ra] = i0 + ra < m ? operand_at(ta, A, a_kc, lda, i0 + ra, k0 + ka) : 0.f;
-      const int rb = b_kc ? t >> 2 : (t & 15) * 4 + e, kb = b_kc ? (t & 3) * 4 + e : t >> 4;
-      Bs[kb][rb] = j0 + rb < n ? operand_at(tb, B, b_kc, ldb, j0 + rb, k0 + kb) : 0.f;
-    }
+    stash8(As, a_kc, t, pa);
+    stash8(Bs, b_kc, t, pb);
     __syncthreads();
+    if (k0 + SK < k) { fetch8(ta, A, a_kc, lda, i0, m, k0 + SK, t, pa); fetch8(tb, B, b_kc, ldb, j0, n, k0 + SK, t, pb); }
 #pragma unroll
     for (int kk = 0; kk < SK; ++kk) {
-      const float4 av = *reinterpret_cast<const float4 *>(&As[kk][tx * 4]);
-      const float4 bv = *reinterpret_cast<const float4 *>(&Bs[kk][ty * 4]);
-      const float a[4] = {av.x, av.y, av.z, av.w}, b[4] = {bv.x, bv.y, bv.z, bv.w};
+      const float4 a0 = *reinterpret_cast<const float4 *>(&As[kk][tx * 4]), a1 = *reinterpret_cast<const float4 *>(&As[kk][64 + tx * 4]);
+      const float4 b0 = *reinterpret_cast<const float4 *>(&Bs[kk][ty * 4]), b1 = *reinterpret_cast<const float4 *>(&Bs[kk][64 + ty * 4]);
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-      for (int x = 0; x < 4; ++x)
+      for (int x = 0; x < 8; ++x)
 #pragma unroll
-        for (int y = 0; y < 4; ++y) acc[x][y] = __fmaf_rn(a[x], b[y], acc[x][y]);
+        for (int y = 0; y < 8; ++y) acc[x][y] = __fmaf_rn(a[x], b[y], acc[x][y]);
     }
     __syncthreads();
   }
@@ -61,10 +104,10 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(int ta, int tb, bool a_k
   const OutScalars r = out_begin(o);
   float mx = 0.f;
 #pragma unroll
-  for (int y = 0; y < 4; ++y)
+  for (int y = 0; y < 8; ++y)
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      const int i = i0 + tx * 4 + x, j = j0 + ty * 4 + y;
+    for (int x = 0; x < 8; ++x) {
+      const int i = i0 + (x < 4 ? tx * 4 + x : 64 + tx * 4 + x - 4), j = j0 + (y < 4 ? ty * 4 + y : 64 + ty * 4 + y - 4);
       if (i < m && j < n) mx = fmaxf(mx, out_store(o, r, i, j, acc[x][y]));
     }
   if (o.amax) block_amax(o.amax, mx);
