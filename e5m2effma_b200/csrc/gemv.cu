@@ -8,7 +8,9 @@
 //     contiguous bytes of each of its rows per step, and the 8 warps split K between them;
 //   * the FP8 bytes are widened to BF16 in registers (exact: at most 4 significant bits) and fed to
 //     mma.sync.m16n8k16 with X as the 8-column operand, so all n <= 8 columns cost the same
-//     instruction stream and the FP32 pipe stays free; products are exact, sums are FP32;
+//     instruction stream and the FP32 pipe stays free; products are exact, sums are FP32.  Where X is
+//     (or converts exactly to) FP16 the same is done in FP16, whose widening costs a quarter of the
+//     instructions (gemv_async16_kernel); FP32 activations run on the FP32 pipe (gemv_fma_kernel);
 //   * the reduction over K may visit k in any order as long as W and X agree, so a lane's 16
 //     contiguous bytes feed four consecutive MMAs without any shuffling;
 //   * the 8 per-warp partial tiles meet in shared memory in a fixed order (deterministic), then one
