@@ -572,18 +572,14 @@ class Sharded:
         self.reduce_amax()
 
     def step_fused(self, i, sptr):
-        """kernel whose epilogue stores into every peer's D, then one small all-reduce (the amax max-reduction where
-        the workload has one, else a one-float sum) after which every rank knows that all blocks have landed"""
+        """kernel whose epilogue stores into every peer's D, then what tells every rank that all blocks have landed: the
+        amax max-all-reduce where the workload has one, else the device-side flag barrier (e5b_peer_barrier: one store
+        per peer and a bounded poll, no collective launched)"""
         self.kernel_bcast(i, sptr)
         if self.amax is not None:
             self.reduce_amax()
         else:
-            self.dist.all_reduce(self._token())
-
-    def _token(self):
-        if not hasattr(self, "_tok"):
-            self._tok = self.torch.zeros(1, device=self.w.dev)
-        return self._tok
+            self.peerbuf.device_barrier(sptr)
 
 
 def measure_sharded(name, w, rot, tm, world, rank, dev, steps, warmup, sampler, t1_ms):

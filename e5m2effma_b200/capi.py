@@ -49,6 +49,8 @@ def _load():
     lib.e5ma_last_error.argtypes = []
     lib.e5b_gemm_fault.restype = ctypes.c_uint
     lib.e5b_gemm_fault.argtypes = []
+    lib.e5b_peer_barrier.restype = ctypes.c_int
+    lib.e5b_peer_barrier.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
     lib.e5b_gemm_bcast.restype = ctypes.c_int
     lib.e5b_gemm_bcast.argtypes = lib.e5ma_gemm.argtypes[:-1] + [ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
     lib.e5b_set_option.restype = ctypes.c_int
@@ -121,6 +123,12 @@ def gemm_bcast(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc, D, 
     arr = (ctypes.c_void_p * max(len(peers), 1))(*peers)
     return lib.e5b_gemm_bcast(transa, transb, m, n, k, alpha, _ref(A), lda, _ref(B), ldb, beta, _ref(C), ldc, _ref(D), ldd,
                               _ref(bias), len(peers), arr, stream)
+
+
+def peer_barrier(rank, flag_ptrs, stream=0):
+    """e5b_peer_barrier: device-side barrier between the ranks whose flag areas are at `flag_ptrs` (indexed by rank)."""
+    arr = (ctypes.c_void_p * len(flag_ptrs))(*flag_ptrs)
+    return lib.e5b_peer_barrier(rank, len(flag_ptrs), arr, stream)
 
 
 def cast(src, dst, count, stream=0):

@@ -294,6 +294,7 @@ cudaError_t launch_gemv_mma(int a_dtype, int x_dtype, const uint8_t *A, int lda,
                             int m, int n, int k, const OutDesc &o, int sms, cudaStream_t s);
 cudaError_t launch_gemm_simt(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const uint8_t *A, int lda,
                              const uint8_t *B, int ldb, int m, int n, int k, const OutDesc &o, cudaStream_t s);
+unsigned int peer_fault_read_and_clear();   // fault word of e5b_peer_barrier's bounded wait (after a device sync)
 unsigned int gemv_fault_read_and_clear();   // fault word of the persistent GEMV's bounded waits (after a device sync)
 // returns cudaErrorNotSupported when the problem is outside what the tensor-core kernel takes
 cudaError_t launch_gemm_tc(int a_dtype, int b_dtype, bool a_kc, bool b_kc, const uint8_t *A, int lda,

@@ -395,3 +395,64 @@ extern "C" e5ma_status e5ma_cast(const e5ma_tensor *src, const e5ma_tensor *dst,
   }
   return cuda_fail(err, "e5ma_cast: kernel launch");
 }
+
+// ---- device-side barrier between the GPUs of a node (declared in include/e5m2effma_b200.h) ----------------------
+// Flag area of a rank: words 0 .. 7 = "rank j has arrived at barrier number e", word 8 = this rank's own count of
+// barriers.  Thread j of the single block: fence, release-store the new count into peer j's word `rank`, then poll
+// this rank's word j until it has reached the count (system-scope acquire loads).  The stores of kernels that ran
+// earlier on the stream (the epilogue broadcast of e5b_gemm_bcast) happen before this kernel starts, the release is
+// cumulative over them, so a peer that has seen the flag sees the data.  The poll is bounded.
+namespace e5b {
+constexpr int PB_MAX_RANKS = 8;
+struct PeerFlags { uint32_t *f[PB_MAX_RANKS]; };
+__device__ unsigned int g_peer_fault;
+
+__global__ void peer_barrier_kernel(int rank, int nranks, PeerFlags p) {
+  __shared__ uint32_t count_s;
+  uint32_t *mine = p.f[rank];
+  if (threadIdx.x == 0) {
+    count_s = mine[PB_MAX_RANKS] + 1u;
+    mine[PB_MAX_RANKS] = count_s;
+  }
+  __syncthreads();
+  const uint32_t count = count_s;
+  const int j = threadIdx.x;
+  if (j >= nranks || j == rank) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.f[j] + rank), "r"(count) : "memory");
+  const unsigned long long t0 = clock64();
+  for (;;) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + j) : "memory");
+    if ((int32_t)(seen - count) >= 0) return;
+    if ((unsigned long long)(clock64() - t0) > 4000000000ull) {
+      atomicCAS(&g_peer_fault, 0u, (uint32_t)(j + 1));
+      return;
+    }
+  }
+}
+
+unsigned int peer_fault_read_and_clear() {
+  unsigned int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_peer_fault, sizeof v) != cudaSuccess) return 0xFFFFFFFFu;
+  if (v) cudaMemcpyToSymbol(g_peer_fault, &zero, sizeof zero);
+  return v;
+}
+}  // namespace e5b
+
+extern "C" e5ma_status e5b_peer_barrier(int rank, int nranks, void *const *flags, cudaStream_t stream) {
+  using namespace e5b;
+  clear_error();
+  if (nranks < 1 || nranks > PB_MAX_RANKS || rank < 0 || rank >= nranks)
+    return fail(E5MA_INVALID_VALUE, "e5b_peer_barrier: rank %d of %d ranks (1 .. %d ranks)", rank, nranks, PB_MAX_RANKS);
+  if (!flags) return fail(E5MA_INVALID_VALUE, "e5b_peer_barrier: flags is NULL");
+  PeerFlags p = {};
+  for (int r = 0; r < nranks; ++r) {
+    if (!flags[r] || ((uintptr_t)flags[r] & 3u)) return fail(E5MA_INVALID_VALUE, "e5b_peer_barrier: flags[%d] is NULL or not 4-byte aligned", r);
+    p.f[r] = (uint32_t *)flags[r];
+  }
+  DeviceProps dp;
+  if (const e5ma_status st = require_blackwell("e5b_peer_barrier", &dp)) return st;
+  peer_barrier_kernel<<<1, 32, 0, stream>>>(rank, nranks, p);
+  return cuda_fail(cudaGetLastError(), "e5b_peer_barrier: kernel launch");
+}

@@ -667,5 +667,6 @@ extern "C" unsigned int e5b_gemm_fault(void) {
   if (cudaMemcpyFromSymbol(&v, e5b::tc::g_fault, sizeof v) != cudaSuccess) return 0xFFFFFFFFu;
   cudaMemcpyToSymbol(e5b::tc::g_fault, &zero, sizeof zero);
   const unsigned int gv = e5b::gemv_fault_read_and_clear();   // the persistent GEMV's waits are bounded the same way
-  return v ? v : (gv ? (gv | 0x80000000u) : 0u);
+  const unsigned int pv = e5b::peer_fault_read_and_clear();   // and e5b_peer_barrier's
+  return v ? v : (gv ? (gv | 0x80000000u) : (pv ? (pv | 0x40000000u) : 0u));
 }

@@ -20,6 +20,8 @@ class PeerBuffer:
     .local      uint8 tensor over this rank's buffer
     .ptrs       device addresses of all ranks' buffers, indexed by group rank (ptrs[rank] is .local)
     .peers(off) addresses of the other ranks' buffers plus a byte offset, in rank order
+    .device_barrier(stream)  e5b_peer_barrier over a flag area kept behind the buffer: every rank's earlier work on
+                its stream is complete and its stores into this rank's buffer are visible (no collective launched)
     """
 
     def __init__(self, nbytes, device, group=None):
@@ -28,14 +30,24 @@ class PeerBuffer:
         self.group = group if group is not None else dist.group.WORLD
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
-        self.local = symm.empty(nbytes, dtype=torch.uint8, device=device)
-        self.handle = symm.rendezvous(self.local, group=self.group)
+        self.flag_off = (nbytes + 255) // 256 * 256          # 64 bytes of barrier flags behind the payload
+        self.whole = symm.empty(self.flag_off + 64, dtype=torch.uint8, device=device)
+        self.whole[self.flag_off:].zero_()
+        torch.cuda.synchronize(device)
+        self.local = self.whole[:nbytes]
+        self.handle = symm.rendezvous(self.whole, group=self.group)      # a collective: every rank's flags are zero after it
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
         if len(self.ptrs) != self.world or self.ptrs[self.rank] != self.local.data_ptr():
             raise RuntimeError("symmetric memory rendezvous returned an unexpected pointer table")
 
     def peers(self, offset=0):
         return [p + offset for r, p in enumerate(self.ptrs) if r != self.rank]
+
+    def device_barrier(self, stream=None):
+        from . import capi
+        sp = torch.cuda.current_stream().cuda_stream if stream is None else stream
+        if capi.peer_barrier(self.rank, [p + self.flag_off for p in self.ptrs], sp) != capi.OK:
+            raise RuntimeError(capi.last_error())
 
     def barrier(self):
         """All ranks' earlier work on their current streams is complete and visible (device-side barrier)."""

@@ -62,6 +62,19 @@ e5ma_status e5b_gemm_bcast(e5ma_op transa, e5ma_op transb, int m, int n, int k, 
                            const e5ma_tensor *C, int ldc, const e5ma_tensor *D, int ldd,
                            const e5ma_tensor *bias, int num_peers, void *const *peer_d, cudaStream_t stream);
 
+/* Device-side barrier between the GPUs of a node, for callers of e5b_gemm_bcast that have no other collective to
+ * close the step with (the amax max-all-reduce of an FP8 output does that job where there is one): enqueues one small
+ * kernel on `stream` that, once everything enqueued before it on this stream has completed, tells every other rank so
+ * (one release store per peer, system scope) and returns when every other rank has told this one.  After it, the blocks
+ * that the peers' e5b_gemm_bcast calls stored into this GPU's buffer are complete and visible to later work on the stream.
+ * flags[r] (r = 0 .. nranks-1, nranks <= 8) is the address, valid on the current device, of rank r's flag area: 16
+ * 32-bit words, zeroed once before the first barrier, mapped on every rank like the output buffers (flags[rank] is this
+ * rank's own).  Every rank must enqueue the same sequence of barriers; the call count is kept in the flag area, so a
+ * barrier can be captured in a CUDA graph and replayed.  The wait is bounded (about two seconds of SM clock): if a
+ * peer never arrives the kernel gives up, the fault shows in e5b_gemm_fault() (bit 30) and the data must not be
+ * trusted.  flags is host memory, read during the call only.  No counterpart in the reference (single device). */
+e5ma_status e5b_peer_barrier(int rank, int nranks, void *const *flags, cudaStream_t stream);
+
 /* One Adam / AdamW step (the arithmetic of e5ma_adam, same cfg) over a list of num_tensors tensors in as
  * few launches as possible: up to 24 tensors share a launch, each block of the grid works on one
  * 16384-element chunk of one tensor.  counts[t] is the element count of tensor t; params, grads, exp_avgs,

@@ -1,7 +1,7 @@
 """Worker of tests/test_gpu_multi.py: one rank per GPU under torch.distributed.run.  Shards a reduced dgrad GEMM
 by column blocks and a reduced decode GEMV by weight rows through the unchanged C interface, gathers the output
 blocks in both ways the library offers -- NCCL all-gather after e5ma_gemm, and e5b_gemm_bcast, whose epilogue stores
-into every peer's buffer -- and compares with the unsharded result computed on the same GPU."""
+into every peer's buffer, closed by the device-side flag barrier e5b_peer_barrier -- and compares with the unsharded result computed on the same GPU."""
 import os
 import sys
 
@@ -65,9 +65,20 @@ def main():
         dist.barrier()
         Dp = capi.Tensor(pb.local.data_ptr() + off, args[13].dtype, args[13].scale_inv, args[13].scale, None, args[13].scaling)
         assert capi.gemm_bcast(*args[:13], Dp, args[14], args[15], pb.peers(off), stream) == capi.OK, capi.last_error()
+        pb.device_barrier(stream)        # e5b_peer_barrier: no host-side barrier, no collective -- the flags alone order the reads below
+        fused = pb.local[: w.D.numel() * es].view(w.D.dtype).view(w.D.shape).clone()
+        torch.cuda.synchronize()
+        # and again into a cleared buffer: the barrier counts its calls
+        dist.barrier()
+        pb.local.zero_()
         torch.cuda.synchronize()
         dist.barrier()
-        fused = pb.local[: w.D.numel() * es].view(w.D.dtype).view(w.D.shape).clone()
+        assert capi.gemm_bcast(*args[:13], Dp, args[14], args[15], pb.peers(off), stream) == capi.OK, capi.last_error()
+        pb.device_barrier(stream)
+        again = pb.local[: w.D.numel() * es].view(w.D.dtype).view(w.D.shape).clone()
+        torch.cuda.synchronize()
+        if not torch.equal(fused.view(torch.uint8), again.view(torch.uint8)):
+            failures.append(f"{name}: second broadcast behind the device-side barrier differs from the first")
 
         if capi.last_route() == plain_route:
             if not torch.equal(nccl.view(torch.uint8), fused.view(torch.uint8)):

@@ -146,3 +146,15 @@ def test_options_and_route_record():
     t = capi.tensor(16, capi.E5M2)
     assert capi.gemm(capi.OP_T, capi.OP_N, 0, 4, 16, 1.0, t, 16, t, 16, 0.0, None, 0, capi.tensor(16, capi.BF16), 1, None) == capi.OK
     assert capi.last_route() == capi.ROUTE_NONE
+
+
+def test_peer_barrier_rejects_bad_arguments():
+    flags = (ctypes.c_void_p * 8)(*([0x1000] * 8))
+    assert capi.lib.e5b_peer_barrier(0, 0, flags, None) == capi.INVALID_VALUE
+    assert capi.lib.e5b_peer_barrier(0, 9, flags, None) == capi.INVALID_VALUE
+    assert capi.lib.e5b_peer_barrier(2, 2, flags, None) == capi.INVALID_VALUE and "rank 2 of 2" in capi.last_error()
+    assert capi.lib.e5b_peer_barrier(0, 2, None, None) == capi.INVALID_VALUE
+    flags[1] = 0
+    assert capi.lib.e5b_peer_barrier(0, 2, flags, None) == capi.INVALID_VALUE and "flags[1]" in capi.last_error()
+    flags[1] = 0x1002
+    assert capi.lib.e5b_peer_barrier(0, 2, flags, None) == capi.INVALID_VALUE
