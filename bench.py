@@ -368,9 +368,12 @@ class Timing:
             ms = float(t.item())
         return ms
 
-    def run(self, step, steps, warmup, graph, sampler=None, graph_optional=False):
+    def run(self, step, steps, warmup, graph, sampler=None, graph_optional=False, min_ms=0.0):
         """step(i, stream_ptr).  graph=True: the K steps are captured once into a CUDA graph and replayed (so that
-        microsecond-scale kernels are not timed behind the Python launch path); steps with NCCL calls run on the stream."""
+        microsecond-scale kernels are not timed behind the Python launch path); steps with NCCL calls run on the stream.
+        min_ms > 0: a graph whose K steps take less than that is replayed several times back to back inside the timed
+        region (the same number of times on every rank) -- with steps that wait for other ranks, the few hundred
+        microseconds by which the ranks' host threads start their replays apart would otherwise be what is timed."""
         torch, stream = self.torch, self.stream
         # W warm-up steps, and more of them until about 10 ms of GPU work have run: after an idle spell the SM clock
         # needs milliseconds to come back up, which a handful of microsecond-scale launches would not cover
@@ -401,10 +404,20 @@ class Timing:
                 g = None
             self.barrier()
         self.timed_as = "cuda_graph" if g is not None else "stream"
+        reps = 1
+        if g is not None and min_ms > 0:
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            p0.record(stream)
+            g.replay()
+            p1.record(stream)
+            self.barrier()
+            reps = max(1, min(64, int(min_ms / max(self.max_over_ranks(p0.elapsed_time(p1)), 1e-3)) + 1))
+        self.replays = reps
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         if g is not None:
-            g.replay()
+            for _ in range(reps):
+                g.replay()
         else:
             for i in range(steps):
                 step(i, stream.cuda_stream)
@@ -412,7 +425,7 @@ class Timing:
         if sampler is not None:
             sampler.poll_until(e1)
         self.barrier()
-        return self.max_over_ranks(e0.elapsed_time(e1)) / steps
+        return self.max_over_ranks(e0.elapsed_time(e1)) / (steps * reps)
 
     def sustained(self, step, est_ms, sampler, seconds=2.0):
         """The same step looped for `seconds`: graph replays of ~30 ms each, NVML sampled from this thread between
@@ -582,13 +595,13 @@ class Sharded:
             self.peerbuf.device_barrier(sptr)
 
 
-def measure_sharded(name, w, rot, tm, world, rank, dev, steps, warmup, sampler, t1_ms):
+def measure_sharded(name, w, rot, tm, world, rank, dev, steps, warmup, sampler, t1_ms, min_ms=0.0):
     """kernel-only and with-collectives time of the sharded workload; T1 / (N * T_N) against the full problem on one GPU."""
     sh = Sharded(name, w, world, rank, dev, rot)
     out = {"sharding": {"c1": "column blocks of B / D", "c2": "column blocks of B / D", "c4": "column blocks of B / D (main_grad stays sharded: no collective)",
                         "c3n1": "weight rows", "c3n8": "weight rows", "c5": "parameter chunks"}.get(name, "element chunks"),
            "full_problem_one_gpu_ms": t1_ms}
-    k_ms = tm.run(sh.kernel, steps, warmup, graph=True)
+    k_ms = tm.run(sh.kernel, steps, warmup, graph=True, min_ms=min_ms)
     out["kernel_only"] = {"ms_per_step": k_ms, "strong_efficiency": t1_ms / (world * k_ms)}
     has_coll = sh.needs_gather or sh.amax is not None
     best = k_ms
@@ -596,18 +609,18 @@ def measure_sharded(name, w, rot, tm, world, rank, dev, steps, warmup, sampler, 
     # CUDA graph (NCCL calls capture); long steps run on the stream as before
     graph_collectives = os.environ.get("E5MA_BENCH_GRAPH_COLLECTIVES", "auto") != "0" and k_ms < 0.2
     if has_coll:
-        n_ms = tm.run(sh.step_nccl, steps, warmup, graph=graph_collectives, sampler=sampler, graph_optional=True)
+        n_ms = tm.run(sh.step_nccl, steps, warmup, graph=graph_collectives, sampler=sampler, graph_optional=True, min_ms=min_ms)
         nccl_timed_as = tm.timed_as
         out["with_collectives_nccl"] = {"ms_per_step": n_ms, "strong_efficiency": t1_ms / (world * n_ms), "timed_as": nccl_timed_as,
                                         "collectives": ("NCCL all-gather of the output (%d bytes)" % sh.gather_bytes if sh.needs_gather else "")
                                         + (" + max-all-reduce of amax" if sh.amax is not None else "")}
         best = n_ms
         if sh.peerbuf is not None:
-            f_ms = tm.run(sh.step_fused, steps, warmup, graph=graph_collectives, sampler=sampler, graph_optional=True)
+            f_ms = tm.run(sh.step_fused, steps, warmup, graph=graph_collectives, sampler=sampler, graph_optional=True, min_ms=min_ms)
             fused_timed_as = tm.timed_as
             out["with_collectives_fused"] = {"ms_per_step": f_ms, "strong_efficiency": t1_ms / (world * f_ms), "timed_as": fused_timed_as,
                                              "collectives": "output blocks stored into every peer's D by the epilogue (e5b_gemm_bcast) + "
-                                             + ("max-all-reduce of amax" if sh.amax is not None else "one-float all-reduce as completion barrier")}
+                                             + ("max-all-reduce of amax" if sh.amax is not None else "device-side flag barrier (e5b_peer_barrier)")}
             best = min(best, f_ms)
         elif sh.peer_note:
             out["with_collectives_fused"] = {"unavailable": sh.peer_note}
@@ -995,7 +1008,7 @@ def main():
                             import oracle as orc
                             entry["observed_error"] = error_report(ow, orc, [(0, 4), (ow.n // 2 - 2, ow.n // 2 + 2)])
                 else:
-                    shd, _ = measure_sharded(other, ow, orot, tm, world, rank, dev, steps_o, 3, osamp, o_t1)
+                    shd, _ = measure_sharded(other, ow, orot, tm, world, rank, dev, steps_o, 3, osamp, o_t1, min_ms=3.0)
                     entry = {"workload": DESC.get(other, other), "ms_per_step": shd["ms_per_step"],
                              "value": ow.units / (shd["ms_per_step"] * 1e-3) / odiv, "unit": ounit, "strong_scaling": shd,
                              "roofline": roofline(other, ow, shd["kernel_only"]["ms_per_step"], pk, units=ow.units / world), "steps": steps_o}
