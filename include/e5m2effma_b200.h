@@ -14,7 +14,8 @@ extern "C" {
  * record which role waited for what; e5ma_gemm has returned E5MA_OK long before, and D is then
  * undefined.  This call waits for all work of the current device (cudaDeviceSynchronize), returns
  * that record (0 = no wait ever ran out) and clears it.  A caller that needs certainty polls it
- * after the GEMMs it cares about.
+ * after the GEMMs it cares about.  The persistent GEMV and e5b_peer_barrier report through the same
+ * call: bit 31 / bit 30 set, with the waiting role or peer in the low bits.
  * No counterpart in the reference, whose kernels have no waits. */
 unsigned int e5b_gemm_fault(void);
 
